@@ -1,0 +1,120 @@
+"""The CPU oracle against every golden vector the reference's own tests hold
+for this path.  These pin the oracle before any CUDA result is compared to it."""
+import numpy as np
+
+
+def test_matmul_4x4_golden(oracle):
+    # crates/sile/tests/backend_matmul.rs:29-64 and llvm_ir_cpu_runtime.rs:53-95
+    a = np.arange(1, 17, dtype=np.float32).reshape(4, 4)
+    b = np.array([1, 0, 2, 1, 0, 1, 3, 2, 1, 0, 4, 3, 0, 1, 5, 4], np.float32).reshape(4, 4)
+    c = np.zeros((4, 4), np.float32)
+    oracle.lib.sile_oracle_bind_matmul(2, 2, 2)
+    oracle.launch("matmul", [a, b, c], grid=(4, 1, 1))
+    expected = np.array([4, 6, 40, 30, 12, 14, 96, 70, 20, 22, 152, 110, 28, 30, 208, 150],
+                        np.float32)
+    assert np.abs(c.ravel() - expected).max() < 1e-4
+    # backend_metal.rs:69-105 asserts the same values exactly
+    assert (c.ravel() == expected).all()
+
+
+def test_matmul_short_grid_leaves_tiles_untouched(oracle):
+    # cpu/codegen.rs:517-533: pids beyond the launched grid never run
+    a = np.arange(1, 17, dtype=np.float32).reshape(4, 4)
+    b = np.eye(4, dtype=np.float32)
+    c = np.full((4, 4), -1.0, np.float32)
+    oracle.lib.sile_oracle_bind_matmul(2, 2, 2)
+    oracle.launch("matmul", [a, b, c], grid=(3, 1, 1))
+    assert (c[:2] == a[:2]).all() and (c[2:, :2] == a[2:, :2]).all()
+    assert (c[2:, 2:] == -1.0).all()
+
+
+def test_matmul_drops_k_remainder(oracle):
+    # lower.rs trip count a.shape[1] / BK is an integer division
+    rng = np.random.default_rng(0)
+    a = rng.uniform(-1, 1, (4, 7)).astype(np.float32)
+    b = rng.uniform(-1, 1, (7, 4)).astype(np.float32)
+    c = oracle.matmul(a, b, 2, 2, 2)
+    want = a[:, :6].astype(np.float64) @ b[:6].astype(np.float64)
+    assert np.abs(c - want).max() < 1e-5
+
+
+def test_matmul_example_procedure(oracle):
+    # crates/sile/examples/matmul.rs:24-56: 128x128x64, tiles 32x16x8, tol 1e-2
+    rng = np.random.default_rng(1)
+    a = rng.random((128, 64), dtype=np.float32)
+    b = rng.random((64, 128), dtype=np.float32)
+    c = oracle.matmul(a, b, 32, 16, 8)
+    assert np.abs(c - a.astype(np.float64) @ b.astype(np.float64)).max() < 1e-2
+
+
+def test_vec_add_golden(oracle):
+    # crates/sile/tests/backend_vec_add.rs:15-24
+    a = np.full(16, 1.0, np.float32)
+    b = np.full(16, 2.0, np.float32)
+    c = np.zeros(16, np.float32)
+    oracle.lib.sile_oracle_bind_vec_add(4)
+    oracle.launch("vec_add", [a, b, c], grid=(4, 1, 1))
+    assert (c == 3.0).all()
+
+
+def test_relu_golden(oracle):
+    # crates/sile/tests/llvm_ir_cpu_runtime.rs:118-140
+    x = np.array([-3.0, -1.0, 0.0, 2.5, 4.0, -7.0, 8.0, -0.5], np.float32)
+    oracle.launch("relu", [x], grid=(1, 1, 1))
+    assert (x == np.array([0, 0, 0, 2.5, 4.0, 0, 8.0, 0], np.float32)).all()
+
+
+def test_softmax_rows_sum_to_one(oracle):
+    # crates/sile/tests/backend_softmax.rs:21-37
+    x = np.arange(32, dtype=np.float32).reshape(4, 8)
+    y = np.zeros((4, 8), np.float32)
+    oracle.lib.sile_oracle_bind_softmax(2, 8)
+    oracle.launch("softmax", [x, y], grid=(2, 1, 1))
+    assert np.abs(y.sum(axis=1) - 1.0).max() < 1e-4
+    e = np.exp(x.astype(np.float64) - x.max(1, keepdims=True))
+    assert np.abs(y - e / e.sum(1, keepdims=True)).max() < 1e-6
+
+
+def test_parallel_reduce_golden(oracle):
+    # crates/sile/tests/backend_parallel_reduce.rs:16-28
+    a = np.ones(100_000, np.float32)
+    out = np.zeros(1, np.float32)
+    oracle.lib.sile_oracle_bind_parallel_reduce(1000)
+    oracle.launch("parallel_reduce", [a, out], grid=(100, 1, 1))
+    assert abs(out[0] - 100_000.0) < 1e-4
+
+
+def test_mlp_example_procedure(oracle):
+    # crates/sile/examples/mlp.rs:60-146: gemm 64^3 tiles 32x32x8 -> matvec -> relu, 1e-3
+    rng = np.random.default_rng(2)
+    w0 = rng.random((64, 64), dtype=np.float32)
+    w1 = rng.random(64, dtype=np.float32)
+    x = rng.random((64, 64), dtype=np.float32)
+    out0 = oracle.matmul(x, w0, 32, 32, 8)
+    out1 = np.zeros(64, np.float32)
+    oracle.lib.sile_oracle_bind_matvec(32, 8)
+    oracle.launch("matvec", [out0, w1, out1], grid=(2, 1, 1))
+    oracle.launch("relu", [out1], grid=(1, 1, 1))
+    want = np.maximum((x.astype(np.float64) @ w0) @ w1, 0)
+    assert np.abs(out1 - want).max() < 1e-3 * max(1.0, np.abs(want).max())
+
+
+def test_attention_matches_f64_softmax_on_small_shapes(oracle):
+    # No reference vector exists for attention (parity unpinned); the composed
+    # oracle is anchored on an independent float64 softmax(QK^T*scale)V.
+    rng = np.random.default_rng(3)
+    bh, s, d = 3, 96, 32
+    q, k, v = (rng.standard_normal((bh * s, d)).astype(np.float32) for _ in range(3))
+    kt = np.ascontiguousarray(k.reshape(bh, s, d).transpose(0, 2, 1)).reshape(bh * d, s)
+    scale = 1.0 / np.sqrt(d)
+    for causal in (False, True):
+        for bm, bn in ((32, 32), (16, 48), (48, 16)):
+            o = oracle.attention(q, kt, v, bh, s, d, bm, bn, scale, causal)
+            sc = np.einsum("bqd,bkd->bqk", q.reshape(bh, s, d).astype(np.float64),
+                           k.reshape(bh, s, d).astype(np.float64)) * scale
+            if causal:
+                sc = np.where(np.tril(np.ones((s, s), bool)), sc, -np.inf)
+            p = np.exp(sc - sc.max(-1, keepdims=True))
+            p /= p.sum(-1, keepdims=True)
+            ref = np.einsum("bqk,bkd->bqd", p, v.reshape(bh, s, d).astype(np.float64))
+            assert np.abs(o - ref.reshape(bh * s, d)).max() < 2e-6
