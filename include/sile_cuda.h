@@ -1,0 +1,147 @@
+/*
+ * libsile_cuda -- B200 (sm_100a) backend for sile's kernel-launch boundary.
+ *
+ * Plain C ABI: pointers and sizes only.  Two families of entry points:
+ *
+ *  1. sile_kernel_<name>: the exact signature sile's CPU backend generates and
+ *     its runtime dlopen()s and calls (host pointers in, results in place,
+ *     complete on return).  A maintainer can point the existing runtime at this
+ *     library unchanged.
+ *  2. sile_cuda_launch / sile_cuda_launch_host: what a `Device::Cuda` arm of
+ *     sile's KernelLauncher::apply would bind -- a kernel description plus
+ *     buffers, with dtype/layout extensions the f32-only reference lacks.
+ *
+ * No entry point falls back to a CPU implementation: without a usable sm_100
+ * device every call fails with SILE_ERR_NO_DEVICE / SILE_ERR_CUDA.
+ */
+#ifndef SILE_CUDA_H
+#define SILE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  They mirror sile_core::Error (crates/sile-core/src/error.rs:2-13):
+ * INVALID ~ Error::Shape, UNSUPPORTED ~ Error::UnsupportedBackend,
+ * NO_DEVICE ~ Error::InvalidDevice, CUDA ~ Error::Io-like runtime failure. */
+#define SILE_OK 0
+#define SILE_ERR_INVALID 1
+#define SILE_ERR_UNSUPPORTED 2
+#define SILE_ERR_CUDA 3
+#define SILE_ERR_TIMEOUT 4 /* a bounded device-side wait ran out; the context stays usable */
+#define SILE_ERR_NO_DEVICE 5
+
+/* Element types.  The reference has F32 only (crates/sile-hir/src/types.rs:11-14);
+ * BF16/F16 are surface extensions. */
+#define SILE_DTYPE_F32 0
+#define SILE_DTYPE_BF16 1
+#define SILE_DTYPE_F16 2
+
+/* Layout of the B operand of a matmul.  The reference is row-major only
+ * (crates/sile-tile-ir/src/lower.rs:991-1002); COL_MAJOR means B[K,N] stored
+ * as [N,K] row-major. */
+#define SILE_LAYOUT_ROW_MAJOR 0
+#define SILE_LAYOUT_COL_MAJOR 1
+
+/* Kernel patterns the backend recognises.  Each is the hand-written equivalent of
+ * one generated unit of the reference (canonical_matmul.rs:24-444 and the per-op
+ * loop nests of crates/sile-tile-ir/src/passes/lowering/). */
+#define SILE_OP_MATMUL 1          /* examples/matmul.rs:3-18 */
+#define SILE_OP_ATTENTION 2       /* composed from mma/reduce_max/exp/reduce_sum tile ops */
+#define SILE_OP_VEC_ADD 3         /* examples/vec_add.rs:3-10 */
+#define SILE_OP_RELU 4            /* examples/mlp.rs:51-55 */
+#define SILE_OP_SOFTMAX 5         /* examples/softmax.rs:3-16 */
+#define SILE_OP_PARALLEL_REDUCE 6 /* examples/parallel_reduce.rs:3-9 */
+#define SILE_OP_MATVEC 7          /* examples/mlp.rs:28-46 */
+
+/* C mirror of what sile_hir::Kernel (crates/sile-hir/src/kernel.rs:9-83) tells a
+ * backend once its body has been recognised: which pattern, the const-generic
+ * values the reference bakes into generated code, and the dtype/layout extensions. */
+typedef struct SileKernelDesc {
+  uint32_t struct_size; /* sizeof(SileKernelDesc), for forward compatibility */
+  int32_t op;           /* SILE_OP_* */
+  int32_t in_dtype;     /* SILE_DTYPE_* of the inputs */
+  int32_t out_dtype;    /* SILE_DTYPE_* of the output */
+  int32_t b_layout;     /* matmul: SILE_LAYOUT_* of B */
+  int32_t causal;       /* attention: 1 = key index <= query index */
+  float scale;          /* attention: softmax scale applied to Q*K^T */
+  int32_t reserved;
+  int64_t consts[4];    /* matmul: BM,BN,BK; vec_add/parallel_reduce: TILE;
+                           softmax: BM,BN; matvec: BM,BK; 0 = unspecified (treated as 1) */
+} SileKernelDesc;
+
+/* ---- 1. exact reference ABI -------------------------------------------------
+ * Replaces the generated `void sile_kernel_<name>(void** buffers,
+ * int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes,
+ * int64_t num_shapes)` (crates/sile-backend/src/cpu/codegen.rs:448-454; caller
+ * crates/sile-backend/src/cpu/mod.rs:12,97-128).  Buffers are HOST float
+ * pointers in kernel-parameter order; shapes is the concatenation of every
+ * argument's shape; the call stages host<->device and is complete on return.
+ * The ABI returns void, as the reference's does: failures are reported through
+ * sile_cuda_last_status() / sile_cuda_last_error() and leave outputs untouched. */
+void sile_kernel_matmul(void** buffers, int64_t num_threadgroups, int64_t threads_per_group,
+                        const int64_t* shapes, int64_t num_shapes);
+void sile_kernel_vec_add(void** buffers, int64_t num_threadgroups, int64_t threads_per_group,
+                         const int64_t* shapes, int64_t num_shapes);
+void sile_kernel_relu(void** buffers, int64_t num_threadgroups, int64_t threads_per_group,
+                      const int64_t* shapes, int64_t num_shapes);
+void sile_kernel_softmax(void** buffers, int64_t num_threadgroups, int64_t threads_per_group,
+                         const int64_t* shapes, int64_t num_shapes);
+void sile_kernel_parallel_reduce(void** buffers, int64_t num_threadgroups, int64_t threads_per_group,
+                                 const int64_t* shapes, int64_t num_shapes);
+void sile_kernel_matvec(void** buffers, int64_t num_threadgroups, int64_t threads_per_group,
+                        const int64_t* shapes, int64_t num_shapes);
+
+/* The reference bakes const generics (tile sizes) into each generated kernel
+ * (crates/sile-tile-ir/src/lower.rs:9-34); the exact ABI has no slot for them.
+ * This binds them for subsequent sile_kernel_<name> calls from the calling
+ * thread.  `name` is the kernel name without the "sile_kernel_" prefix. */
+int sile_cuda_bind_consts(const char* name, const int64_t* consts, int64_t num_consts);
+
+/* ---- 2. Device::Cuda launch ---------------------------------------------------
+ * The arm crates/sile/src/kernel_launcher.rs:69-71 leaves unimplemented, shaped
+ * after the one GPU precedent, MetalBackend::execute_llir(func, param_kinds,
+ * args, launch, stream) (crates/sile-backend/src/metal/mod.rs:65-76).
+ * dev_buffers are DEVICE pointers in kernel-parameter order; shapes as above;
+ * grid is LaunchConfig::grid (crates/sile-core/src/kernel.rs:4-6) -- only its
+ * product matters, as in cpu/mod.rs:109-120; stream is a cudaStream_t (NULL =
+ * default stream).  Asynchronous: returns after enqueueing. */
+int sile_cuda_launch(const SileKernelDesc* desc, void* const* dev_buffers, const int64_t* shapes,
+                     int64_t num_shapes, const uint32_t grid[3], void* stream);
+
+/* Same launch with HOST buffers: stages inputs to the device, runs, copies
+ * outputs (the last buffer; for relu the only buffer) back, and returns when
+ * complete -- what MetalBackend::execute_llir does around its dispatch
+ * (crates/sile-backend/src/metal/mod.rs:117-125,160-169). */
+int sile_cuda_launch_host(const SileKernelDesc* desc, void* const* host_buffers, const int64_t* shapes,
+                          int64_t num_shapes, const uint32_t grid[3]);
+
+/* Device selection, after Device::cuda(index) (crates/sile-core/src/device.rs:23-35).
+ * Fails with SILE_ERR_NO_DEVICE when the index does not name an sm_100 GPU. */
+int sile_cuda_set_device(int index);
+int sile_cuda_device_count(void);
+
+/* Stream::synchronize (crates/sile-core/src/stream.rs:17-19), a no-op in the
+ * reference, is real here.  Also reports a device-side time-out recorded since
+ * the last call (SILE_ERR_TIMEOUT) and clears it. */
+int sile_cuda_synchronize(void* stream);
+
+/* Scratch the f32 matmul needs on the device for a given problem, in bytes
+ * (0 for 16-bit inputs).  sile_cuda_launch obtains it from the stream-ordered
+ * allocator itself; the figure is exposed for capacity planning. */
+size_t sile_cuda_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int32_t in_dtype);
+
+/* Message / code of the calling thread's most recent failure ("" / SILE_OK if none). */
+const char* sile_cuda_last_error(void);
+int sile_cuda_last_status(void);
+
+/* Library version: major*10000 + minor*100 + patch. */
+int sile_cuda_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SILE_CUDA_H */

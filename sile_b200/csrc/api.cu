@@ -1,0 +1,473 @@
+// extern "C" surface of libsile_cuda.so (declared in include/sile_cuda.h).
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "internal.h"
+
+namespace sile {
+namespace {
+
+thread_local std::string t_last_error;
+thread_local int t_last_status = SILE_OK;
+
+// Const generics bound for the exact-ABI entry points, per calling thread.
+struct BoundConsts {
+  int64_t matmul[3] = {1, 1, 1};
+  int64_t vec_add[1] = {4};  // the tile the reference's example hard-codes (examples/vec_add.rs:6)
+  int64_t softmax[2] = {1, 0};  // BN = 0: whole row
+  int64_t parallel_reduce[1] = {1};
+  int64_t matvec[2] = {1, 1};
+};
+thread_local BoundConsts t_consts;
+
+std::mutex g_status_mutex;
+int* g_status_words[64] = {nullptr};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+std::once_flag g_encode_once;
+
+int check_device() {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(SILE_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+  }
+  static thread_local int checked_dev = -1;
+  if (checked_dev == dev) return SILE_OK;
+  int major = 0;
+  e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(SILE_ERR_NO_DEVICE, "cannot query device %d: %s", dev, cudaGetErrorString(e));
+  }
+  if (major != 10) return fail(SILE_ERR_NO_DEVICE, "device %d is sm_%d0; this library is built for sm_100a only", dev, major);
+  checked_dev = dev;
+  return SILE_OK;
+}
+
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  t_last_error = buf;
+  t_last_status = code;
+  return code;
+}
+
+int device_status_word(int** out) {
+  int dev = 0;
+  SILE_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(SILE_ERR_INVALID, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (!g_status_words[dev]) {
+    int* p = nullptr;
+    SILE_CUDA_TRY(cudaMalloc(&p, sizeof(int)));
+    SILE_CUDA_TRY(cudaMemset(p, 0, sizeof(int)));
+    g_status_words[dev] = p;
+  }
+  *out = g_status_words[dev];
+  return SILE_OK;
+}
+
+int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank, const void* base, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle) {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    else
+      cudaGetLastError();
+  });
+  if (!g_encode_tiled) return fail(SILE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[5];
+  cuuint32_t bx[5];
+  cuuint32_t es[5];
+  for (uint32_t i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) gstr[i] = strides_bytes[i];
+  }
+  CUresult r = g_encode_tiled(map, dtype, rank, const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(SILE_ERR_INVALID, "cuTensorMapEncodeTiled failed (%d): base %p dims [%llu,%llu] stride %llu box [%u,%u]",
+                static_cast<int>(r), base, static_cast<unsigned long long>(dims[0]),
+                static_cast<unsigned long long>(rank > 1 ? dims[1] : 0),
+                static_cast<unsigned long long>(rank > 1 ? strides_bytes[0] : 0), box[0], rank > 1 ? box[1] : 0);
+  return SILE_OK;
+}
+
+namespace {
+
+size_t dtype_size(int dt) { return dt == SILE_DTYPE_F32 ? 4 : 2; }
+
+int64_t grid_product(const uint32_t grid[3]) {
+  return static_cast<int64_t>(grid[0]) * static_cast<int64_t>(grid[1]) * static_cast<int64_t>(grid[2]);
+}
+
+int64_t const_or_one(const SileKernelDesc* d, int i) { return d->consts[i] > 0 ? d->consts[i] : 1; }
+
+// Buffers of a launch as (pointer, element count, element size, is_output).
+struct ArgSpan {
+  size_t bytes;
+  bool is_input;
+  bool is_output;
+};
+
+// Validates shapes for `desc` and lists the byte size / direction of every buffer.
+int describe_args(const SileKernelDesc* d, const int64_t* shapes, int64_t ns, std::vector<ArgSpan>* out) {
+  out->clear();
+  const size_t in_sz = dtype_size(d->in_dtype), out_sz = dtype_size(d->out_dtype);
+  auto pos = [&](int64_t v) { return v > 0; };
+  switch (d->op) {
+    case SILE_OP_MATMUL: {
+      if (ns != 6) return fail(SILE_ERR_INVALID, "matmul: expected 6 shape entries (a[M,K] b[K,N] c[M,N]), got %lld", (long long)ns);
+      const int64_t m = shapes[0], k = shapes[1], n = shapes[5];
+      if (!pos(m) || !pos(k) || !pos(n)) return fail(SILE_ERR_INVALID, "matmul: non-positive dimension");
+      if (shapes[2] != k || shapes[3] != n || shapes[4] != m)
+        return fail(SILE_ERR_INVALID, "matmul: inconsistent shapes a[%lld,%lld] b[%lld,%lld] c[%lld,%lld]", (long long)shapes[0],
+                    (long long)shapes[1], (long long)shapes[2], (long long)shapes[3], (long long)shapes[4], (long long)shapes[5]);
+      out->push_back({static_cast<size_t>(m * k) * in_sz, true, false});
+      out->push_back({static_cast<size_t>(k * n) * in_sz, true, false});
+      out->push_back({static_cast<size_t>(m * n) * out_sz, true, true});  // untouched tiles must survive the round trip
+      return SILE_OK;
+    }
+    case SILE_OP_ATTENTION: {
+      if (ns % 4 != 0 || ns / 4 < 2 || ns / 4 > 4) return fail(SILE_ERR_INVALID, "attention: expected 4 buffers of rank 2..4");
+      const int64_t r = ns / 4;
+      int64_t elems = 1;
+      for (int64_t i = 0; i < r; ++i) {
+        if (!pos(shapes[i])) return fail(SILE_ERR_INVALID, "attention: non-positive dimension");
+        elems *= shapes[i];
+      }
+      for (int64_t a = 1; a < 4; ++a)
+        for (int64_t i = 0; i < r; ++i)
+          if (shapes[a * r + i] != shapes[i]) return fail(SILE_ERR_INVALID, "attention: q, k, v, o must share one shape");
+      for (int a = 0; a < 3; ++a) out->push_back({static_cast<size_t>(elems) * in_sz, true, false});
+      out->push_back({static_cast<size_t>(elems) * out_sz, false, true});
+      return SILE_OK;
+    }
+    case SILE_OP_VEC_ADD: {
+      if (ns != 3) return fail(SILE_ERR_INVALID, "vec_add: expected 3 rank-1 buffers");
+      if (!pos(shapes[0]) || shapes[1] != shapes[0] || shapes[2] != shapes[0]) return fail(SILE_ERR_INVALID, "vec_add: lengths differ");
+      out->push_back({static_cast<size_t>(shapes[0]) * 4, true, false});
+      out->push_back({static_cast<size_t>(shapes[0]) * 4, true, false});
+      out->push_back({static_cast<size_t>(shapes[0]) * 4, true, true});
+      return SILE_OK;
+    }
+    case SILE_OP_RELU: {
+      if (ns != 1 || !pos(shapes[0])) return fail(SILE_ERR_INVALID, "relu: expected one rank-1 buffer");
+      out->push_back({static_cast<size_t>(shapes[0]) * 4, true, true});
+      return SILE_OK;
+    }
+    case SILE_OP_SOFTMAX: {
+      if (ns != 4) return fail(SILE_ERR_INVALID, "softmax: expected x[R,C] y[R,C]");
+      if (!pos(shapes[0]) || !pos(shapes[1]) || shapes[2] != shapes[0] || shapes[3] != shapes[1])
+        return fail(SILE_ERR_INVALID, "softmax: x and y shapes differ");
+      out->push_back({static_cast<size_t>(shapes[0] * shapes[1]) * 4, true, false});
+      out->push_back({static_cast<size_t>(shapes[0] * shapes[1]) * 4, true, true});
+      return SILE_OK;
+    }
+    case SILE_OP_PARALLEL_REDUCE: {
+      if (ns != 2 || !pos(shapes[0]) || shapes[1] != 1) return fail(SILE_ERR_INVALID, "parallel_reduce: expected a[N] out[1]");
+      out->push_back({static_cast<size_t>(shapes[0]) * 4, true, false});
+      out->push_back({4, true, true});  // atomic_add accumulates onto the caller's value
+      return SILE_OK;
+    }
+    case SILE_OP_MATVEC: {
+      if (ns != 4) return fail(SILE_ERR_INVALID, "matvec: expected x[M,K] y[K] z[M]");
+      if (!pos(shapes[0]) || !pos(shapes[1]) || shapes[2] != shapes[1] || shapes[3] != shapes[0])
+        return fail(SILE_ERR_INVALID, "matvec: inconsistent shapes");
+      out->push_back({static_cast<size_t>(shapes[0] * shapes[1]) * 4, true, false});
+      out->push_back({static_cast<size_t>(shapes[1]) * 4, true, false});
+      out->push_back({static_cast<size_t>(shapes[0]) * 4, true, true});
+      return SILE_OK;
+    }
+    default:
+      return fail(SILE_ERR_UNSUPPORTED, "backend not implemented for op %d", d->op);
+  }
+}
+
+int launch_device(const SileKernelDesc* d, void* const* buf, const int64_t* shapes, int64_t ns, int64_t ntg, cudaStream_t stream) {
+  const bool f32_only = d->in_dtype == SILE_DTYPE_F32 && d->out_dtype == SILE_DTYPE_F32;
+  switch (d->op) {
+    case SILE_OP_MATMUL: {
+      GemmProblem p;
+      p.a = buf[0]; p.b = buf[1]; p.c = buf[2];
+      p.m = shapes[0]; p.k = shapes[1]; p.n = shapes[5];
+      p.in_dtype = d->in_dtype; p.out_dtype = d->out_dtype; p.b_layout = d->b_layout;
+      p.bm = const_or_one(d, 0); p.bn = const_or_one(d, 1); p.bk = const_or_one(d, 2);
+      p.num_threadgroups = ntg;
+      const size_t ws = gemm_workspace_bytes(p);
+      void* wsp = nullptr;
+      if (ws) {
+        SILE_CUDA_TRY(cudaMallocAsync(&wsp, ws, stream));
+        p.workspace = wsp;
+        p.workspace_bytes = ws;
+      }
+      const int rc = gemm_launch(p, stream);
+      if (wsp) {
+        cudaError_t e = cudaFreeAsync(wsp, stream);
+        if (rc == SILE_OK && e != cudaSuccess) return fail(SILE_ERR_CUDA, "cudaFreeAsync failed: %s", cudaGetErrorString(e));
+      }
+      return rc;
+    }
+    case SILE_OP_ATTENTION: {
+      const int64_t r = ns / 4;
+      AttnProblem p;
+      p.q = buf[0]; p.k = buf[1]; p.v = buf[2]; p.o = buf[3];
+      p.d = shapes[r - 1];
+      p.s = shapes[r - 2];
+      p.bh = 1;
+      for (int64_t i = 0; i + 2 < r; ++i) p.bh *= shapes[i];
+      p.scale = d->scale;
+      p.causal = d->causal;
+      if (d->in_dtype != SILE_DTYPE_BF16 || d->out_dtype != SILE_DTYPE_BF16)
+        return fail(SILE_ERR_UNSUPPORTED, "attention: bf16 in / bf16 out only");
+      return attention_launch(p, stream);
+    }
+    case SILE_OP_VEC_ADD: {
+      if (!f32_only) return fail(SILE_ERR_UNSUPPORTED, "vec_add: f32 only");
+      // Tiles [0, grid) of TILE elements each are computed (cpu/codegen.rs:517-533).
+      const int64_t tile = const_or_one(d, 0);
+      const int64_t n = std::min<int64_t>(shapes[0] / tile, ntg) * tile;
+      return vec_add_launch(static_cast<const float*>(buf[0]), static_cast<const float*>(buf[1]), static_cast<float*>(buf[2]), n, stream);
+    }
+    case SILE_OP_RELU: {
+      if (!f32_only) return fail(SILE_ERR_UNSUPPORTED, "relu: f32 only");
+      if (ntg < 1) return SILE_OK;
+      return relu_launch(static_cast<float*>(buf[0]), shapes[0], stream);
+    }
+    case SILE_OP_SOFTMAX: {
+      if (!f32_only) return fail(SILE_ERR_UNSUPPORTED, "softmax: f32 only");
+      const int64_t rows = shapes[2], cols = shapes[3];
+      const int64_t bm = const_or_one(d, 0);
+      const int64_t bn = d->consts[1] > 0 ? d->consts[1] : cols;
+      if (bn != cols) return fail(SILE_ERR_UNSUPPORTED, "softmax: BN (%lld) must span the row (%lld columns)", (long long)bn, (long long)cols);
+      const int64_t r = std::min<int64_t>(rows / bm, ntg) * bm;
+      return softmax_rows_launch(static_cast<const float*>(buf[0]), shapes[1], static_cast<float*>(buf[1]), cols, r, cols, stream);
+    }
+    case SILE_OP_PARALLEL_REDUCE: {
+      if (!f32_only) return fail(SILE_ERR_UNSUPPORTED, "parallel_reduce: f32 only");
+      const int64_t tile = const_or_one(d, 0);
+      const int64_t n = std::min<int64_t>(shapes[0] / tile, ntg) * tile;
+      return reduce_sum_launch(static_cast<const float*>(buf[0]), n, static_cast<float*>(buf[1]), stream);
+    }
+    case SILE_OP_MATVEC: {
+      if (!f32_only) return fail(SILE_ERR_UNSUPPORTED, "matvec: f32 only");
+      const int64_t bm = const_or_one(d, 0), bk = const_or_one(d, 1);
+      const int64_t m = std::min<int64_t>(shapes[0] / bm, ntg) * bm;
+      const int64_t k = shapes[1] / bk * bk;
+      if (k != shapes[1]) return fail(SILE_ERR_UNSUPPORTED, "matvec: K must be a multiple of BK");
+      return matvec_launch(static_cast<const float*>(buf[0]), static_cast<const float*>(buf[1]), static_cast<float*>(buf[2]), m, shapes[1], stream);
+    }
+    default:
+      return fail(SILE_ERR_UNSUPPORTED, "backend not implemented for op %d", d->op);
+  }
+}
+
+int validate_desc(const SileKernelDesc* d) {
+  if (!d) return fail(SILE_ERR_INVALID, "null kernel description");
+  if (d->struct_size != sizeof(SileKernelDesc))
+    return fail(SILE_ERR_INVALID, "SileKernelDesc size %u does not match this library (%zu)", d->struct_size, sizeof(SileKernelDesc));
+  return SILE_OK;
+}
+
+int read_and_clear_status() {
+  int* word = nullptr;
+  if (int rc = device_status_word(&word)) return rc;
+  int v = 0;
+  SILE_CUDA_TRY(cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost));
+  if (v != 0) {
+    SILE_CUDA_TRY(cudaMemset(word, 0, sizeof(int)));
+    return fail(v, "a device-side wait ran out (code %d); results of the affected launch are invalid", v);
+  }
+  return SILE_OK;
+}
+
+int launch_host(const SileKernelDesc* d, void* const* host, const int64_t* shapes, int64_t ns, int64_t ntg) {
+  if (int rc = validate_desc(d)) return rc;
+  if (int rc = check_device()) return rc;
+  if (!host || !shapes) return fail(SILE_ERR_INVALID, "null argument");
+  std::vector<ArgSpan> args;
+  if (int rc = describe_args(d, shapes, ns, &args)) return rc;
+  cudaStream_t stream = nullptr;
+  SILE_CUDA_TRY(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  std::vector<void*> dev(args.size(), nullptr);
+  int rc = SILE_OK;
+  auto cleanup = [&]() {
+    for (void* p : dev)
+      if (p) cudaFreeAsync(p, stream);
+    cudaStreamSynchronize(stream);
+    cudaStreamDestroy(stream);
+  };
+  for (size_t i = 0; i < args.size() && rc == SILE_OK; ++i) {
+    if (!host[i]) { rc = fail(SILE_ERR_INVALID, "null buffer %zu", i); break; }
+    cudaError_t e = cudaMallocAsync(&dev[i], std::max<size_t>(args[i].bytes, 16), stream);
+    if (e != cudaSuccess) { rc = fail(SILE_ERR_CUDA, "device allocation of %zu bytes failed: %s", args[i].bytes, cudaGetErrorString(e)); break; }
+    if (args[i].is_input) {
+      e = cudaMemcpyAsync(dev[i], host[i], args[i].bytes, cudaMemcpyHostToDevice, stream);
+      if (e != cudaSuccess) rc = fail(SILE_ERR_CUDA, "host->device copy failed: %s", cudaGetErrorString(e));
+    }
+  }
+  if (rc == SILE_OK) rc = launch_device(d, dev.data(), shapes, ns, ntg, stream);
+  if (rc == SILE_OK) {
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) rc = fail(SILE_ERR_CUDA, "kernel execution failed: %s", cudaGetErrorString(e));
+  }
+  if (rc == SILE_OK) rc = read_and_clear_status();
+  for (size_t i = 0; i < args.size() && rc == SILE_OK; ++i) {
+    if (args[i].is_output) {
+      cudaError_t e = cudaMemcpyAsync(host[i], dev[i], args[i].bytes, cudaMemcpyDeviceToHost, stream);
+      if (e != cudaSuccess) rc = fail(SILE_ERR_CUDA, "device->host copy failed: %s", cudaGetErrorString(e));
+    }
+  }
+  if (rc == SILE_OK) {
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) rc = fail(SILE_ERR_CUDA, "device->host copy failed: %s", cudaGetErrorString(e));
+  }
+  cleanup();
+  if (rc == SILE_OK) t_last_status = SILE_OK;
+  return rc;
+}
+
+SileKernelDesc f32_desc(int op) {
+  SileKernelDesc d;
+  std::memset(&d, 0, sizeof(d));
+  d.struct_size = sizeof(d);
+  d.op = op;
+  d.in_dtype = SILE_DTYPE_F32;
+  d.out_dtype = SILE_DTYPE_F32;
+  d.b_layout = SILE_LAYOUT_ROW_MAJOR;
+  d.scale = 1.0f;
+  return d;
+}
+
+}  // namespace
+}  // namespace sile
+
+using namespace sile;
+
+extern "C" {
+
+int sile_cuda_version(void) { return 100; }
+
+const char* sile_cuda_last_error(void) { return t_last_error.c_str(); }
+int sile_cuda_last_status(void) { return t_last_status; }
+
+int sile_cuda_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+int sile_cuda_set_device(int index) {
+  int n = sile_cuda_device_count();
+  if (index < 0 || index >= n) return fail(SILE_ERR_NO_DEVICE, "invalid device: cuda:%d (%d visible)", index, n);
+  SILE_CUDA_TRY(cudaSetDevice(index));
+  return check_device();
+}
+
+int sile_cuda_synchronize(void* stream) {
+  if (int rc = check_device()) return rc;
+  SILE_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  return read_and_clear_status();
+}
+
+size_t sile_cuda_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int32_t in_dtype) {
+  GemmProblem p;
+  p.m = m; p.n = n; p.k = k; p.in_dtype = in_dtype;
+  return gemm_workspace_bytes(p);
+}
+
+int sile_cuda_bind_consts(const char* name, const int64_t* consts, int64_t n) {
+  if (!name || (!consts && n > 0)) return fail(SILE_ERR_INVALID, "null argument");
+  auto set = [&](int64_t* dst, int64_t want) -> int {
+    if (n != want) return fail(SILE_ERR_INVALID, "%s takes %lld const generics, got %lld", name, (long long)want, (long long)n);
+    for (int64_t i = 0; i < want; ++i) {
+      if (consts[i] <= 0) return fail(SILE_ERR_INVALID, "%s: const generic %lld must be positive", name, (long long)i);
+      dst[i] = consts[i];
+    }
+    return SILE_OK;
+  };
+  if (!std::strcmp(name, "matmul") || !std::strcmp(name, "gemm")) return set(t_consts.matmul, 3);
+  if (!std::strcmp(name, "vec_add")) return set(t_consts.vec_add, 1);
+  if (!std::strcmp(name, "softmax")) return set(t_consts.softmax, 2);
+  if (!std::strcmp(name, "parallel_reduce")) return set(t_consts.parallel_reduce, 1);
+  if (!std::strcmp(name, "matvec")) return set(t_consts.matvec, 2);
+  return fail(SILE_ERR_UNSUPPORTED, "no kernel named %s", name);
+}
+
+int sile_cuda_launch(const SileKernelDesc* desc, void* const* dev_buffers, const int64_t* shapes, int64_t num_shapes,
+                     const uint32_t grid[3], void* stream) {
+  if (int rc = validate_desc(desc)) return rc;
+  if (int rc = check_device()) return rc;
+  if (!dev_buffers || !shapes || !grid) return fail(SILE_ERR_INVALID, "null argument");
+  std::vector<ArgSpan> args;
+  if (int rc = describe_args(desc, shapes, num_shapes, &args)) return rc;
+  for (size_t i = 0; i < args.size(); ++i)
+    if (!dev_buffers[i]) return fail(SILE_ERR_INVALID, "null buffer %zu", i);
+  const int rc = launch_device(desc, dev_buffers, shapes, num_shapes, grid_product(grid), static_cast<cudaStream_t>(stream));
+  if (rc == SILE_OK) t_last_status = SILE_OK;
+  return rc;
+}
+
+int sile_cuda_launch_host(const SileKernelDesc* desc, void* const* host_buffers, const int64_t* shapes, int64_t num_shapes,
+                          const uint32_t grid[3]) {
+  if (!grid) return fail(SILE_ERR_INVALID, "null argument");
+  return launch_host(desc, host_buffers, shapes, num_shapes, grid_product(grid));
+}
+
+void sile_kernel_matmul(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {
+  SileKernelDesc d = f32_desc(SILE_OP_MATMUL);
+  for (int i = 0; i < 3; ++i) d.consts[i] = t_consts.matmul[i];
+  launch_host(&d, buffers, shapes, num_shapes, num_threadgroups * threads_per_group);
+}
+void sile_kernel_vec_add(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {
+  SileKernelDesc d = f32_desc(SILE_OP_VEC_ADD);
+  d.consts[0] = t_consts.vec_add[0];
+  launch_host(&d, buffers, shapes, num_shapes, num_threadgroups * threads_per_group);
+}
+void sile_kernel_relu(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {
+  SileKernelDesc d = f32_desc(SILE_OP_RELU);
+  launch_host(&d, buffers, shapes, num_shapes, num_threadgroups * threads_per_group);
+}
+void sile_kernel_softmax(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {
+  SileKernelDesc d = f32_desc(SILE_OP_SOFTMAX);
+  d.consts[0] = t_consts.softmax[0];
+  d.consts[1] = t_consts.softmax[1];
+  launch_host(&d, buffers, shapes, num_shapes, num_threadgroups * threads_per_group);
+}
+void sile_kernel_parallel_reduce(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {
+  SileKernelDesc d = f32_desc(SILE_OP_PARALLEL_REDUCE);
+  d.consts[0] = t_consts.parallel_reduce[0];
+  launch_host(&d, buffers, shapes, num_shapes, num_threadgroups * threads_per_group);
+}
+void sile_kernel_matvec(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {
+  SileKernelDesc d = f32_desc(SILE_OP_MATVEC);
+  d.consts[0] = t_consts.matvec[0];
+  d.consts[1] = t_consts.matvec[1];
+  launch_host(&d, buffers, shapes, num_shapes, num_threadgroups * threads_per_group);
+}
+
+}  // extern "C"

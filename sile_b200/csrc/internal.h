@@ -1,0 +1,73 @@
+// Declarations shared by the translation units of libsile_cuda.so.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/sile_cuda.h"
+
+namespace sile {
+
+// Records a message retrievable through sile_cuda_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+
+#define SILE_CUDA_TRY(expr)                                                              \
+  do {                                                                                   \
+    cudaError_t _e = (expr);                                                             \
+    if (_e != cudaSuccess)                                                               \
+      return ::sile::fail(SILE_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                 \
+                          cudaGetErrorString(_e), __FILE__, __LINE__);                   \
+  } while (0)
+
+// Per-device status word written by kernels whose bounded waits ran out.
+// Allocated on first use for the current device; never freed.
+int device_status_word(int** out);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry-point lookup (no link
+// dependency on libcuda).  Strides are in bytes and exclude the innermost one.
+int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank, const void* base,
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                      CUtensorMapSwizzle swizzle);
+
+// ---- GEMM -----------------------------------------------------------------------
+struct GemmProblem {
+  const void* a = nullptr;   // [M,K] row-major, f32 or bf16/f16
+  const void* b = nullptr;   // f32: [K,N] row-major; 16-bit: per b_layout
+  void* c = nullptr;         // [M,N] row-major
+  int64_t m = 0, n = 0, k = 0;
+  int in_dtype = SILE_DTYPE_F32;
+  int out_dtype = SILE_DTYPE_F32;
+  int b_layout = SILE_LAYOUT_ROW_MAJOR;
+  // Logical tile of the kernel definition and the number of launched tiles: they decide
+  // which part of C is written (whole tiles only, K remainder dropped), never the CTA tiling.
+  int64_t bm = 1, bn = 1, bk = 1;
+  int64_t num_threadgroups = INT64_MAX;
+  void* workspace = nullptr;  // device scratch for the f32 split; see gemm_workspace_bytes
+  size_t workspace_bytes = 0;
+};
+size_t gemm_workspace_bytes(const GemmProblem& p);
+int gemm_launch(const GemmProblem& p, cudaStream_t stream);
+
+// ---- attention forward ----------------------------------------------------------
+struct AttnProblem {
+  const void* q = nullptr;  // [BH, S, D] bf16
+  const void* k = nullptr;  // [BH, S, D] bf16
+  const void* v = nullptr;  // [BH, S, D] bf16
+  void* o = nullptr;        // [BH, S, D] bf16
+  int64_t bh = 0, s = 0, d = 0;
+  float scale = 1.0f;
+  int causal = 0;
+};
+int attention_launch(const AttnProblem& p, cudaStream_t stream);
+
+// ---- standalone tile ops (HBM-bound) --------------------------------------------
+int vec_add_launch(const float* a, const float* b, float* c, int64_t n, cudaStream_t stream);
+int relu_launch(float* x, int64_t n, cudaStream_t stream);
+int softmax_rows_launch(const float* x, int64_t ldx, float* y, int64_t ldy, int64_t rows, int64_t cols,
+                        cudaStream_t stream);
+int reduce_sum_launch(const float* a, int64_t n, float* out, cudaStream_t stream);
+int matvec_launch(const float* x, const float* y, float* z, int64_t m, int64_t k, cudaStream_t stream);
+
+}  // namespace sile

@@ -1,0 +1,235 @@
+// Standalone tile ops of the reference's examples as HBM-bound kernels:
+// 128-bit vectorised, coalesced, grids sized in multiples of the SM count.
+// Each replaces one generated scalar loop nest of the reference's lowering
+// (crates/sile-tile-ir/src/passes/lowering/{tile_expr.rs,tile_compute/reduce.rs,
+// tile_compute/fused_reduce.rs,block_scalar.rs}).
+#include <algorithm>
+
+#include "internal.h"
+
+namespace sile {
+namespace {
+
+constexpr int kThreads = 256;
+
+int sm_count() {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+
+int grid_for(int64_t work_items, int per_sm) {
+  const int sms = sm_count();
+  const int64_t blocks = (work_items + kThreads - 1) / kThreads;
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks, static_cast<int64_t>(sms) * per_sm)));
+}
+
+// c = a + b   (examples/vec_add.rs:3-10; tile_expr.rs pointwise store)
+__global__ void vec_add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c, int64_t n, int vec) {
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  if (vec) {
+    const int64_t n4 = n >> 2;
+    const float4* a4 = reinterpret_cast<const float4*>(a);
+    const float4* b4 = reinterpret_cast<const float4*>(b);
+    float4* c4 = reinterpret_cast<float4*>(c);
+    for (int64_t i = tid; i < n4; i += nthreads) {
+      const float4 x = __ldcs(a4 + i), y = __ldcs(b4 + i);
+      __stcs(c4 + i, make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w));
+    }
+    for (int64_t i = (n4 << 2) + tid; i < n; i += nthreads) c[i] = a[i] + b[i];
+  } else {
+    for (int64_t i = tid; i < n; i += nthreads) c[i] = a[i] + b[i];
+  }
+}
+
+// x = max_tile(0, x) = (0 >= x) ? 0 : x   (lower.rs:619-641; examples/mlp.rs:51-55)
+__device__ __forceinline__ float relu_sel(float v) { return (0.0f >= v) ? 0.0f : v; }
+__global__ void relu_kernel(float* __restrict__ x, int64_t n, int vec) {
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  if (vec) {
+    const int64_t n4 = n >> 2;
+    float4* x4 = reinterpret_cast<float4*>(x);
+    for (int64_t i = tid; i < n4; i += nthreads) {
+      float4 v = x4[i];
+      v.x = relu_sel(v.x); v.y = relu_sel(v.y); v.z = relu_sel(v.z); v.w = relu_sel(v.w);
+      x4[i] = v;
+    }
+    for (int64_t i = (n4 << 2) + tid; i < n; i += nthreads) x[i] = relu_sel(x[i]);
+  } else {
+    for (int64_t i = tid; i < n; i += nthreads) x[i] = relu_sel(x[i]);
+  }
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Row softmax (examples/softmax.rs:3-16): y = exp(x - max) / sum(exp(x - max)).
+// One warp per row for short rows; the row is read once from HBM when it fits the
+// per-lane register cache (cols <= 32 * kCache), otherwise it is re-read from L2.
+constexpr int kCache = 32;
+__global__ void softmax_rows_kernel(const float* __restrict__ x, int64_t ldx, float* __restrict__ y, int64_t ldy, int64_t rows,
+                                    int cols) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int64_t warp_global = blockIdx.x * static_cast<int64_t>(warps_per_block) + (threadIdx.x >> 5);
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps_per_block;
+  for (int64_t row = warp_global; row < rows; row += nwarps) {
+    const float* xr = x + row * ldx;
+    float* yr = y + row * ldy;
+    float cache[kCache];
+    const bool cached = cols <= 32 * kCache;
+    float mx = -INFINITY;
+    if (cached) {
+#pragma unroll
+      for (int i = 0; i < kCache; ++i) {
+        const int c = lane + 32 * i;
+        cache[i] = c < cols ? xr[c] : -INFINITY;
+        mx = fmaxf(mx, cache[i]);
+      }
+    } else {
+      for (int c = lane; c < cols; c += 32) mx = fmaxf(mx, xr[c]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    if (cached) {
+#pragma unroll
+      for (int i = 0; i < kCache; ++i) {
+        const int c = lane + 32 * i;
+        cache[i] = c < cols ? expf(cache[i] - mx) : 0.0f;
+        sum += cache[i];
+      }
+    } else {
+      for (int c = lane; c < cols; c += 32) sum += expf(xr[c] - mx);
+    }
+    sum = warp_sum(sum);
+    if (cached) {
+#pragma unroll
+      for (int i = 0; i < kCache; ++i) {
+        const int c = lane + 32 * i;
+        if (c < cols) yr[c] = cache[i] / sum;
+      }
+    } else {
+      for (int c = lane; c < cols; c += 32) yr[c] = expf(xr[c] - mx) / sum;
+    }
+  }
+}
+
+// out[0] += sum(a[0..n))   (examples/parallel_reduce.rs:3-9: per-tile reduce_sum then
+// atomic_add; block_scalar.rs:98-157).  One red.global.add.f32 per block; the order of
+// the atomics is nondeterministic here as it is under OpenMP in the reference.
+__global__ void reduce_sum_kernel(const float* __restrict__ a, int64_t n, float* __restrict__ out, int vec) {
+  __shared__ float partial[32];
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  float acc = 0.0f;
+  if (vec) {
+    const int64_t n4 = n >> 2;
+    const float4* a4 = reinterpret_cast<const float4*>(a);
+    float acc2 = 0.0f;
+    int64_t i = tid;
+    for (; i + nthreads < n4; i += 2 * nthreads) {
+      const float4 v = __ldcs(a4 + i);
+      const float4 w = __ldcs(a4 + i + nthreads);
+      acc += (v.x + v.y) + (v.z + v.w);
+      acc2 += (w.x + w.y) + (w.z + w.w);
+    }
+    for (; i < n4; i += nthreads) {
+      const float4 v = __ldcs(a4 + i);
+      acc += (v.x + v.y) + (v.z + v.w);
+    }
+    acc += acc2;
+    for (int64_t j = (n4 << 2) + tid; j < n; j += nthreads) acc += a[j];
+  } else {
+    for (int64_t i = tid; i < n; i += nthreads) acc += a[i];
+  }
+  acc = warp_sum(acc);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) partial[warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    float v = lane < (blockDim.x >> 5) ? partial[lane] : 0.0f;
+    v = warp_sum(v);
+    if (lane == 0) atomicAdd(out, v);
+  }
+}
+
+// z[r] = sum_k x[r,k] * y[k]   (examples/mlp.rs:28-46).  One warp per row, float4 loads.
+__global__ void matvec_kernel(const float* __restrict__ x, const float* __restrict__ y, float* __restrict__ z, int64_t m, int64_t k,
+                              int vec) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int64_t warp_global = blockIdx.x * static_cast<int64_t>(warps_per_block) + (threadIdx.x >> 5);
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps_per_block;
+  for (int64_t row = warp_global; row < m; row += nwarps) {
+    const float* xr = x + row * k;
+    float acc = 0.0f;
+    if (vec) {
+      const int64_t k4 = k >> 2;
+      const float4* x4 = reinterpret_cast<const float4*>(xr);
+      const float4* y4 = reinterpret_cast<const float4*>(y);
+      for (int64_t i = lane; i < k4; i += 32) {
+        const float4 a = __ldcs(x4 + i);
+        const float4 b = __ldg(y4 + i);
+        acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+      }
+    } else {
+      for (int64_t i = lane; i < k; i += 32) acc += xr[i] * y[i];
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) z[row] = acc;
+  }
+}
+
+bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+}  // namespace
+
+int vec_add_launch(const float* a, const float* b, float* c, int64_t n, cudaStream_t stream) {
+  if (n <= 0) return SILE_OK;
+  const int vec = aligned16(a) && aligned16(b) && aligned16(c);
+  vec_add_kernel<<<grid_for((n + 3) / 4, 8), kThreads, 0, stream>>>(a, b, c, n, vec);
+  SILE_CUDA_TRY(cudaGetLastError());
+  return SILE_OK;
+}
+
+int relu_launch(float* x, int64_t n, cudaStream_t stream) {
+  if (n <= 0) return SILE_OK;
+  relu_kernel<<<grid_for((n + 3) / 4, 8), kThreads, 0, stream>>>(x, n, aligned16(x));
+  SILE_CUDA_TRY(cudaGetLastError());
+  return SILE_OK;
+}
+
+int softmax_rows_launch(const float* x, int64_t ldx, float* y, int64_t ldy, int64_t rows, int64_t cols, cudaStream_t stream) {
+  if (rows <= 0) return SILE_OK;
+  if (cols > (1ll << 30)) return fail(SILE_ERR_INVALID, "softmax: row too long");
+  softmax_rows_kernel<<<grid_for(rows * 32, 8), kThreads, 0, stream>>>(x, ldx, y, ldy, rows, static_cast<int>(cols));
+  SILE_CUDA_TRY(cudaGetLastError());
+  return SILE_OK;
+}
+
+int reduce_sum_launch(const float* a, int64_t n, float* out, cudaStream_t stream) {
+  if (n <= 0) return SILE_OK;
+  reduce_sum_kernel<<<grid_for((n + 3) / 4, 4), kThreads, 0, stream>>>(a, n, out, aligned16(a));
+  SILE_CUDA_TRY(cudaGetLastError());
+  return SILE_OK;
+}
+
+int matvec_launch(const float* x, const float* y, float* z, int64_t m, int64_t k, cudaStream_t stream) {
+  if (m <= 0) return SILE_OK;
+  const int vec = aligned16(x) && aligned16(y) && (k % 4 == 0);
+  matvec_kernel<<<grid_for(m * 32, 8), kThreads, 0, stream>>>(x, y, z, m, k, vec);
+  SILE_CUDA_TRY(cudaGetLastError());
+  return SILE_OK;
+}
+
+}  // namespace sile

@@ -1,0 +1,81 @@
+"""The C-ABI library loads and exports every symbol include/sile_cuda.h declares
+(no compute: runs without a GPU)."""
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import sile_b200
+    sile_b200.build()
+    return sile_b200._lib.lib()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "sile_cuda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sile_(?:kernel|cuda)_\w+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(lib):
+    import sile_b200
+    declared = _declared_symbols()
+    assert declared, "no declarations found"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in sile_cuda.h but not exported"
+    assert set(declared) == set(sile_b200._lib.EXPORTED_SYMBOLS)
+
+
+def test_version_and_error_string(lib):
+    assert lib.sile_cuda_version() >= 100
+    assert isinstance(lib.sile_cuda_last_error(), bytes)
+
+
+def test_bind_consts_validation(lib):
+    import ctypes as C
+    import sile_b200
+    arr = (C.c_int64 * 3)(2, 2, 2)
+    assert lib.sile_cuda_bind_consts(b"matmul", arr, 3) == 0
+    assert lib.sile_cuda_bind_consts(b"matmul", arr, 2) == sile_b200._lib.ERR_INVALID
+    assert lib.sile_cuda_bind_consts(b"nonesuch", arr, 3) == sile_b200._lib.ERR_UNSUPPORTED
+    bad = (C.c_int64 * 3)(2, 0, 2)
+    assert lib.sile_cuda_bind_consts(b"matmul", bad, 3) == sile_b200._lib.ERR_INVALID
+    assert b"positive" in lib.sile_cuda_last_error()
+
+
+def test_desc_and_shape_validation_precede_device_use(lib):
+    import ctypes as C
+    import sile_b200
+    d = sile_b200.make_desc(sile_b200._lib.OP_MATMUL)
+    d.struct_size = 4
+    grid = (C.c_uint32 * 3)(1, 1, 1)
+    rc = lib.sile_cuda_launch_host(C.byref(d), None, None, 0, grid)
+    assert rc == sile_b200._lib.ERR_INVALID
+
+
+def test_no_cpu_fallback_without_device(lib):
+    """Without a GPU the compute entry points fail loudly instead of computing on the host."""
+    import numpy as np
+    import torch
+    import sile_b200
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    a = np.ones((4, 4), np.float32)
+    c = np.zeros((4, 4), np.float32)
+    with pytest.raises(sile_b200.SileError) as e:
+        sile_b200.kernel_call("matmul", [a, a, c], grid=(4, 1, 1))
+    assert e.value.code in (sile_b200._lib.ERR_NO_DEVICE, sile_b200._lib.ERR_CUDA)
+    assert (c == 0).all()
+
+
+def test_product_never_imports_oracle():
+    pkg = os.path.join(ROOT, "sile_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in src.lower(), f"{f} mentions the oracle"
