@@ -1,4 +1,401 @@
+// Fused attention forward O = softmax(scale * Q K^T [+ causal mask]) V for sm_100a,
+// bf16 in/out, head_dim 128, f32 softmax statistics.
+//
+// The reference has no attention kernel; this is the fused form of the op sequence its
+// DSL would compose from mma / reduce_max / exp / reduce_sum tile ops
+// (crates/sile-tile-ir/src/lower.rs:509-748; general mma path
+// crates/sile-tile-ir/src/passes/lowering/tile_compute/mma.rs:25-260): online softmax over
+// 128-key blocks with the running row max m, row sum l and an unnormalised accumulator.
+//
+// One CTA = one (batch*head, 256-query block) = two 128-row Q tiles, 12 warps:
+//   warp 0        TMA producer: Q tiles once, then K_j / V_j through 2-stage rings
+//   warp 1        MMA issuer:   S_t = Q_t K_j^T (smem x smem) and O_t += P_t V_j
+//                 (P_t read from TMEM, V_j MN-major from smem), f32 accumulators in TMEM
+//   warps 4..7    softmax of Q tile 0 (thread r owns row r = TMEM lane r)
+//   warps 8..11   softmax of Q tile 1
+// TMEM (512 columns): S0 | S1 | O0 | O1, 128 columns each; P_t (bf16 pairs) overwrites the
+// first 64 columns of S_t.  The issue order S0 S1 | PV0 S0' PV1 S1' ... lets the softmax of one
+// tile run under the MMAs of the other.  O is rescaled only when the row max has grown by more
+// than 2^8 since the last rescale; the same (stale) max is used for P and l, so the result is
+// unchanged.  The rescale and the final 1/l normalisation are done by the softmax warps.
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
 #include "internal.h"
+#include "ptx.cuh"
+
 namespace sile {
-int attention_launch(const AttnProblem&, cudaStream_t) { return fail(SILE_ERR_UNSUPPORTED, "attention: not built yet"); }
+namespace {
+
+using namespace ptx;
+
+constexpr int kD = 128;            // head dim
+constexpr int kTileQ = 128;        // rows per Q tile (= TMEM lanes)
+constexpr int kBlockQ = 2 * kTileQ;
+constexpr int kBlockKV = 128;
+constexpr int kPanelBytes = 128 * 64 * 2;   // one [128 rows x 64 cols] 128B-swizzled panel
+constexpr int kTileBytes = 2 * kPanelBytes;  // [128 x 128] bf16
+constexpr int kStagesKV = 2;
+constexpr int kThreads = 384;
+constexpr int kSmemQ = 0;
+constexpr int kSmemK = kSmemQ + 2 * kTileBytes;
+constexpr int kSmemV = kSmemK + kStagesKV * kTileBytes;
+constexpr int kSmemBar = kSmemV + kStagesKV * kTileBytes;
+constexpr int kSmemBytes = kSmemBar + 256 + 1024;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct AttnParams {
+  int s;          // sequence length
+  int bh;         // batch * heads
+  int num_qblocks;
+  int causal;
+  float scale_log2;  // scale * log2(e)
+  int64_t row_stride;  // elements between consecutive rows of O (= D)
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
+
+// Number of 128-key blocks Q tile `t` of this CTA attends to (0 = tile is past the end).
+__device__ __forceinline__ int kv_blocks_for_tile(const AttnParams& p, int q0) {
+  if (q0 >= p.s) return 0;
+  const int all = (p.s + kBlockKV - 1) / kBlockKV;
+  if (!p.causal) return all;
+  const int last_q = min(q0 + kTileQ, p.s) - 1;
+  return min(all, last_q / kBlockKV + 1);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
+                const __grid_constant__ CUtensorMap tma_v, __nv_bfloat16* __restrict__ o, const AttnParams p,
+                int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar);
+  uint64_t* q_full = bars;           // [2]
+  uint64_t* k_full = bars + 2;       // [2]
+  uint64_t* k_empty = bars + 4;      // [2]
+  uint64_t* v_full = bars + 6;       // [2]
+  uint64_t* v_empty = bars + 8;      // [2]
+  uint64_t* s_full = bars + 10;      // [2] S_t written by the tensor core
+  uint64_t* p_full = bars + 12;      // [2] P_t written (and O_t rescaled) by the softmax warps
+  uint64_t* o_done = bars + 14;      // [2] O_t += P_t V_j finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
+
+  // heavy (late) query blocks first so the causal tail is short
+  const int bh = blockIdx.x % p.bh;
+  const int qblk = p.num_qblocks - 1 - blockIdx.x / p.bh;
+  const int q_base = qblk * kBlockQ;
+  const int n_kv[2] = {kv_blocks_for_tile(p, q_base), kv_blocks_for_tile(p, q_base + kTileQ)};
+  const int n_max = max(n_kv[0], n_kv[1]);
+
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tma_q);
+    prefetch_tensormap(&tma_k);
+    prefetch_tensormap(&tma_v);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], kTileQ);
+      mbar_init(&o_done[i], 1);
+    }
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(tmem_slot, kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tmem_o[2] = {tmem_base + 256, tmem_base + 384};
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      bool ok = true;
+      auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int row0) {
+        mbar_expect_tx(bar, kTileBytes);
+        tma_load_3d(dst, map, bar, 0, row0, bh);
+        tma_load_3d(dst + kPanelBytes, map, bar, 64, row0, bh);
+      };
+      if (n_kv[0] > 0) load_tile(&tma_q, smem + kSmemQ, &q_full[0], q_base);
+      if (n_max > 0) load_tile(&tma_k, smem + kSmemK, &k_full[0], 0);
+      if (n_kv[1] > 0) load_tile(&tma_q, smem + kSmemQ + kTileBytes, &q_full[1], q_base + kTileQ);
+      if (n_max > 0) load_tile(&tma_v, smem + kSmemV, &v_full[0], 0);
+      for (int j = 1; j < n_max && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_empty[st], ph ^ 1u, status, SILE_ERR_TIMEOUT)) { ok = false; break; }
+        load_tile(&tma_k, smem + kSmemK + st * kTileBytes, &k_full[st], j * kBlockKV);
+        if (!mbar_wait(&v_empty[st], ph ^ 1u, status, SILE_ERR_TIMEOUT)) { ok = false; break; }
+        load_tile(&tma_v, smem + kSmemV + st * kTileBytes, &v_full[st], j * kBlockKV);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0 && n_max > 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(kTileQ, kBlockKV, true, false, false);  // Q K^T: both K-major
+      constexpr uint32_t idesc_o = make_idesc_f16(kTileQ, kD, true, false, true);         // P V: V is MN-major
+      const uint32_t q_addr = smem_u32(smem + kSmemQ);
+      const uint32_t k_addr = smem_u32(smem + kSmemK);
+      const uint32_t v_addr = smem_u32(smem + kSmemV);
+      bool ok = true;
+
+      auto issue_s = [&](int t, int st) {
+        // S_t = Q_t (128 x 128, two 64-wide k panels) * K_st^T
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+          const uint64_t da = make_smem_desc_sw128(q_addr + t * kTileBytes + off, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(k_addr + st * kTileBytes + off, 16, 1024);
+          umma_ss_f16<1>(tmem_s[t], da, db, idesc_s, kk != 0 ? 1u : 0u);
+        }
+        umma_commit<1>(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int st, bool accumulate) {
+        // O_t += P_t (TMEM, 8 columns per 16 keys) * V_st (rows = keys, 2048 B per 16 keys; d panels 16 KiB apart)
+#pragma unroll
+        for (int kk = 0; kk < kBlockKV / 16; ++kk) {
+          const uint64_t db = make_smem_desc_sw128(v_addr + st * kTileBytes + kk * 2048, kPanelBytes, 1024);
+          umma_ts_f16(tmem_o[t], tmem_s[t] + kk * 8, db, idesc_o, (accumulate || kk != 0) ? 1u : 0u);
+        }
+        umma_commit<1>(&o_done[t]);
+      };
+
+      // prologue: S_0 for both tiles
+      if (n_kv[0] > 0) ok = ok && mbar_wait(&q_full[0], 0, status, SILE_ERR_TIMEOUT);
+      ok = ok && mbar_wait(&k_full[0], 0, status, SILE_ERR_TIMEOUT);
+      if (ok) {
+        tcgen05_fence_after();
+        if (n_kv[0] > 0) issue_s(0, 0);
+        if (n_kv[1] > 0) {
+          ok = mbar_wait(&q_full[1], 0, status, SILE_ERR_TIMEOUT);
+          if (ok) {
+            tcgen05_fence_after();
+            issue_s(1, 0);
+          }
+        }
+        umma_commit<1>(&k_empty[0]);
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int st_n = (j + 1) & 1;
+        const uint32_t ph_n = ((j + 1) >> 1) & 1;
+        if (!mbar_wait(&v_full[st], ph, status, SILE_ERR_TIMEOUT)) { ok = false; break; }
+        if (j < n_kv[0]) {
+          if (!mbar_wait(&p_full[0], j & 1, status, SILE_ERR_TIMEOUT)) { ok = false; break; }
+          tcgen05_fence_after();
+          issue_pv(0, st, j > 0);
+        }
+        if (j + 1 < n_max) {
+          if (!mbar_wait(&k_full[st_n], ph_n, status, SILE_ERR_TIMEOUT)) { ok = false; break; }
+          tcgen05_fence_after();
+        }
+        if (j + 1 < n_kv[0]) issue_s(0, st_n);
+        if (j < n_kv[1]) {
+          if (!mbar_wait(&p_full[1], j & 1, status, SILE_ERR_TIMEOUT)) { ok = false; break; }
+          tcgen05_fence_after();
+          issue_pv(1, st, j > 0);
+        }
+        umma_commit<1>(&v_empty[st]);
+        if (j + 1 < n_kv[1]) issue_s(1, st_n);
+        if (j + 1 < n_max) umma_commit<1>(&k_empty[st_n]);
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 4) {
+    // ---------------- softmax / correction / epilogue ----------------
+    const int t = (warp - 4) >> 2;        // Q tile of this warpgroup
+    const int quarter = warp & 3;         // TMEM lane quarter of this warp
+    const int row_in_tile = quarter * 32 + lane;
+    const int q_idx = q_base + t * kTileQ + row_in_tile;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t ts = tmem_s[t] + lane_off;
+    const uint32_t to = tmem_o[t] + lane_off;
+    const int n = n_kv[t];
+    float m_used = -INFINITY;  // row max (scaled, log2 domain) that P, l and O currently refer to
+    float l = 0.0f;
+    bool ok = true;
+
+    for (int j = 0; j < n; ++j) {
+      if (!mbar_wait(&s_full[t], j & 1, status, SILE_ERR_TIMEOUT)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(ts + c * 32, sr[c]);
+      tcgen05_wait_ld();
+
+      const int kv0 = j * kBlockKV;
+      const bool need_mask = (kv0 + kBlockKV > p.s) || (p.causal && kv0 + kBlockKV - 1 > q_base + t * kTileQ);
+      if (need_mask) {
+        const int limit = p.causal ? min(q_idx, p.s - 1) : p.s - 1;  // last visible key index
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (kv0 + c * 32 + i > limit) sr[c][i] = 0xff800000u;  // -inf
+      }
+
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        mx0 = fmaxf(mx0, __uint_as_float(sr[0][i]));
+        mx1 = fmaxf(mx1, __uint_as_float(sr[1][i]));
+        mx2 = fmaxf(mx2, __uint_as_float(sr[2][i]));
+        mx3 = fmaxf(mx3, __uint_as_float(sr[3][i]));
+      }
+      const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      const float m_new = fmaxf(m_used, m_blk);
+      const bool rescale = (m_new - m_used > kRescaleThreshold) || (m_used == -INFINITY);  // NaN-safe: inf - (-inf)
+      float alpha = 1.0f;
+      if (rescale) {
+        alpha = (m_used == -INFINITY) ? 0.0f : ex2(m_used - m_new);
+        m_used = m_new;
+      }
+      const float m_sub = (m_used == -INFINITY) ? 0.0f : m_used;
+
+      if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+        // O_t of block j-1 is complete whenever S_t of block j is (MMAs retire in issue order);
+        // the wait gives the tcgen05 -> thread ordering for the accumulator.
+        if (!mbar_wait(&o_done[t], (j - 1) & 1, status, SILE_ERR_TIMEOUT)) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tcgen05_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t orow[32];
+          tmem_ld_32x32b_x32(to + c * 32, orow);
+          tcgen05_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+          tmem_st_32x32b_x32(to + c * 32, orow);
+        }
+        tcgen05_wait_st();
+      }
+
+      float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = ex2(fmaf(__uint_as_float(sr[c][2 * i]), p.scale_log2, -m_sub));
+          const float p1 = ex2(fmaf(__uint_as_float(sr[c][2 * i + 1]), p.scale_log2, -m_sub));
+          sum0 += p0;
+          sum1 += p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x32b_x16(ts + c * 16, pk);
+      }
+      l = l * alpha + (sum0 + sum1);
+      tcgen05_wait_st();
+      tcgen05_fence_before();
+      mbar_arrive(&p_full[t]);
+    }
+
+    if (ok && n > 0) {
+      if (!mbar_wait(&o_done[t], (n - 1) & 1, status, SILE_ERR_TIMEOUT)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tcgen05_fence_after();
+        const float inv_l = 1.0f / l;
+        __nv_bfloat16* dst = o + (static_cast<int64_t>(bh) * p.s + q_idx) * p.row_stride;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t orow[32];
+          tmem_ld_32x32b_x32(to + c * 32, orow);
+          tcgen05_wait_ld();
+          if (q_idx < p.s) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(orow[8 * i]) * inv_l, __uint_as_float(orow[8 * i + 1]) * inv_l);
+              v.y = pack_bf16x2(__uint_as_float(orow[8 * i + 2]) * inv_l, __uint_as_float(orow[8 * i + 3]) * inv_l);
+              v.z = pack_bf16x2(__uint_as_float(orow[8 * i + 4]) * inv_l, __uint_as_float(orow[8 * i + 5]) * inv_l);
+              v.w = pack_bf16x2(__uint_as_float(orow[8 * i + 6]) * inv_l, __uint_as_float(orow[8 * i + 7]) * inv_l);
+              d4[i] = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    if (*reinterpret_cast<volatile int*>(status) != 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) {
+      }
+    }
+    tmem_dealloc<1>(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+int attention_launch(const AttnProblem& a, cudaStream_t stream) {
+  if (!a.q || !a.k || !a.v || !a.o) return fail(SILE_ERR_INVALID, "attention: null buffer");
+  if (a.bh <= 0 || a.s <= 0) return fail(SILE_ERR_INVALID, "attention: non-positive dimension");
+  if (a.d != kD) return fail(SILE_ERR_UNSUPPORTED, "attention: head_dim %lld not supported (128 only)", (long long)a.d);
+  if (a.s > (1 << 24) || a.bh > (1 << 24)) return fail(SILE_ERR_INVALID, "attention: dimension too large");
+  for (const void* ptr : {a.q, a.k, a.v, static_cast<const void*>(a.o)})
+    if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(SILE_ERR_UNSUPPORTED, "attention: buffers must be 16-byte aligned");
+  if (!(a.scale > 0.0f)) return fail(SILE_ERR_INVALID, "attention: scale must be positive");
+
+  int* status = nullptr;
+  if (int rc = device_status_word(&status)) return rc;
+
+  CUtensorMap tq, tk, tv;
+  const uint64_t dims[3] = {static_cast<uint64_t>(kD), static_cast<uint64_t>(a.s), static_cast<uint64_t>(a.bh)};
+  const uint64_t strides[2] = {static_cast<uint64_t>(kD) * 2, static_cast<uint64_t>(a.s) * kD * 2};
+  const uint32_t box[3] = {64, 128, 1};
+  if (int rc = encode_tensor_map(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.q, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = encode_tensor_map(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.k, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = encode_tensor_map(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.v, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+
+  AttnParams p{};
+  p.s = static_cast<int>(a.s);
+  p.bh = static_cast<int>(a.bh);
+  p.num_qblocks = static_cast<int>((a.s + kBlockQ - 1) / kBlockQ);
+  p.causal = a.causal ? 1 : 0;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.row_stride = kD;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    SILE_CUDA_TRY(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    attr_set = true;
+  }
+  const int64_t grid = static_cast<int64_t>(p.bh) * p.num_qblocks;
+  if (grid > 0x7fffffffll) return fail(SILE_ERR_INVALID, "attention: too many blocks");
+  attn_fwd_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, stream>>>(tq, tk, tv, static_cast<__nv_bfloat16*>(a.o), p, status);
+  SILE_CUDA_TRY(cudaGetLastError());
+  return SILE_OK;
+}
+
+}  // namespace sile

@@ -1,0 +1,145 @@
+"""Attention-forward parity: the sm_100a kernel through the C ABI against the composed CPU
+oracle (no reference vector exists for attention: parity unpinned, see oracle/sile_oracle.h).
+
+Tolerance: max-abs error <= 2e-2 of the output scale (bf16 in/out, f32 accumulation)."""
+import numpy as np
+import pytest
+
+from _util import rel_err
+
+pytestmark = pytest.mark.gpu
+BF16_TOL = 2e-2
+
+
+@pytest.fixture(scope="module")
+def sb():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import sile_b200
+    return sile_b200
+
+
+def _inputs(bh, s, d, seed):
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return [torch.randn(bh, s, d, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+            for _ in range(3)]
+
+
+def _oracle_units(oracle, q, k, v, heads, s, d, scale, causal, units_per_head, bm=128):
+    """Runs the oracle on the listed heads; returns {(head, q_tile): [bm, d] rows}."""
+    out = {}
+    for h in heads:
+        qh = q[h].float().cpu().numpy().reshape(s, d)
+        kt = np.ascontiguousarray(k[h].float().cpu().numpy().reshape(s, d).T)
+        vh = v[h].float().cpu().numpy().reshape(s, d)
+        tiles = units_per_head[h] if units_per_head is not None else None
+        o = oracle.attention(qh, kt, vh, 1, s, d, bm, 64, scale, causal, tiles)
+        for t in (tiles if tiles is not None else range(s // bm)):
+            out[(h, int(t))] = o[t * bm:(t + 1) * bm]
+    return out
+
+
+@pytest.mark.parametrize("bh,s", [(2, 256), (3, 384), (1, 128), (2, 1024)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_small_full(sb, oracle, bh, s, causal):
+    import torch
+    d, scale = 128, 1.0 / np.sqrt(128)
+    q, k, v = _inputs(bh, s, d, 100 + s)
+    o = torch.zeros_like(q)
+    sb.attention(q, k, v, o, scale, causal).apply()
+    sb.synchronize()
+    kt = np.ascontiguousarray(k.float().cpu().numpy().transpose(0, 2, 1)).reshape(bh * d, s)
+    want = oracle.attention(q.float().cpu().numpy().reshape(bh * s, d), kt,
+                            v.float().cpu().numpy().reshape(bh * s, d), bh, s, d, 64, 64, scale, causal)
+    assert rel_err(o.float().cpu().numpy().reshape(bh * s, d), want) < BF16_TOL
+
+
+@pytest.mark.parametrize("s", [1, 100, 200, 333, 1000])
+@pytest.mark.parametrize("causal", [False, True])
+def test_ragged_sequence(sb, causal, s):
+    # lengths that are not multiples of the key block / query tile: checked against float64
+    import torch
+    bh, d, scale = 2, 128, 0.11
+    q, k, v = _inputs(bh, s, d, 7 + s)
+    o = torch.full_like(q, 3.0)
+    sb.attention(q, k, v, o, scale, causal).apply()
+    sb.synchronize()
+    sc = torch.einsum("bqd,bkd->bqk", q.double(), k.double()) * scale
+    if causal:
+        sc = sc.masked_fill(~torch.tril(torch.ones(s, s, dtype=torch.bool, device="cuda")), float("-inf"))
+    want = torch.einsum("bqk,bkd->bqd", torch.softmax(sc, -1), v.double())
+    assert rel_err(o.double().cpu().numpy(), want.cpu().numpy()) < BF16_TOL
+
+
+def test_rank4_shapes_and_rows_sum_to_one(sb):
+    # V = 1 makes every output element the softmax row sum
+    import torch
+    q, k, _ = _inputs(8, 512, 128, 5)
+    q, k = q.view(2, 4, 512, 128), k.view(2, 4, 512, 128)
+    v = torch.ones_like(q)
+    o = torch.zeros_like(q)
+    sb.attention(q, k, v, o, 0.3, True).apply()
+    sb.synchronize()
+    assert (o.float() - 1.0).abs().max().item() < 1e-2
+
+
+def test_large_logits_and_rescale_path(sb):
+    # scores whose row max keeps growing by more than the lazy-rescale threshold
+    import torch
+    bh, s, d = 1, 1024, 128
+    q, k, v = _inputs(bh, s, d, 11)
+    ramp = torch.linspace(0.0, 6.0, s, device="cuda").view(1, s, 1)
+    k = (k.float() * 0.2 + ramp * q.float().mean(dim=1, keepdim=True).sign()).to(torch.bfloat16)
+    o = torch.zeros_like(q)
+    sb.attention(q, k, v, o, 1.0, False).apply()
+    sb.synchronize()
+    sc = torch.einsum("bqd,bkd->bqk", q.double(), k.double())
+    want = torch.einsum("bqk,bkd->bqd", torch.softmax(sc, -1), v.double())
+    assert rel_err(o.double().cpu().numpy(), want.cpu().numpy()) < BF16_TOL
+
+
+def test_rejects_unsupported(sb):
+    import torch
+    q = torch.zeros(2, 128, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(sb.SileError) as e:
+        sb.attention(q, q, q, torch.zeros_like(q), 1.0).apply()
+    assert e.value.code == sb._lib.ERR_UNSUPPORTED
+    q = torch.zeros(2, 128, 128, device="cuda", dtype=torch.float32)
+    with pytest.raises(sb.SileError):
+        sb.attention(q, q, q, torch.zeros_like(q), 1.0).apply()
+
+
+def _sampled_config(sb, oracle, b, h, s, causal, seed):
+    import torch
+    d, scale = 128, 1.0 / np.sqrt(128)
+    bh = b * h
+    q, k, v = _inputs(bh, s, d, seed)
+    o = torch.zeros_like(q)
+    sb.attention(q.view(b, h, s, d), k.view(b, h, s, d), v.view(b, h, s, d), o.view(b, h, s, d), scale, causal).apply()
+    sb.synchronize()
+    rng = np.random.default_rng(0)
+    heads = sorted(set(int(x) for x in rng.choice(bh, size=4, replace=False)))
+    n_tiles = s // 128
+    units = {hd: sorted(set([n_tiles - 1] + [int(x) for x in rng.choice(n_tiles, size=2, replace=False)])) for hd in heads}
+    want = _oracle_units(oracle, q, k, v, heads, s, d, scale, causal, units)
+    worst = 0.0
+    for (hd, t), rows in want.items():
+        got = o[hd, t * 128:(t + 1) * 128].float().cpu().numpy()
+        worst = max(worst, rel_err(got, rows))
+    assert worst < BF16_TOL
+    # linearity in V at full size: O(2V) == 2 O(V) exactly (power-of-two scaling commutes with rounding)
+    o2 = torch.zeros_like(q)
+    sb.attention(q, k, (v * 2).contiguous(), o2, scale, causal).apply()
+    sb.synchronize()
+    assert torch.equal(o2, o * 2)
+
+
+def test_a4_noncausal_b4_h32_s4096_sampled(sb, oracle):
+    _sampled_config(sb, oracle, 4, 32, 4096, False, 0)
+
+
+def test_a5_causal_shard_h32_s8192_sampled(sb, oracle):
+    # one GPU's shard of the batch 8 x 32 heads configuration: 32 (batch, head) pairs
+    _sampled_config(sb, oracle, 1, 32, 8192, True, 1)

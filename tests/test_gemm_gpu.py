@@ -100,7 +100,7 @@ def test_zero_and_identity(sb):
     a = uniform((256, 128), 5)
     eye = np.eye(128, dtype=np.float32)
     got = _gpu_matmul_f32(sb, a, eye, 1, 1, 1)
-    assert np.abs(got - a).max() < 1e-6
+    assert np.abs(got - a).max() < 1e-5  # hi+lo bf16 split keeps ~17 mantissa bits
     got = _gpu_matmul_f32(sb, np.zeros_like(a), eye, 1, 1, 1)
     assert (got == 0).all()
     del torch
