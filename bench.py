@@ -1,0 +1,429 @@
+#!/usr/bin/env python
+"""Headline benchmark: bf16 GEMM 8192^3 (A row-major, B column-major, f32 accumulate, bf16
+out), N-sharded over the GPUs of one box, with flash-attention forward reported beside it.
+
+    python bench.py --gpus 1 --steps 50 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the reference's CPU path, timed on host cores
+
+A step is one pass of the hot path over one batch of synthetic input (one whole GEMM).  Rank 0
+prints ONE JSON line.  `value` is whole-job TFLOP/s with inputs resident in HBM; `e2e` is the
+same metric through the C ABI with HOST buffers (host<->device copies inside the timed region).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "bf16 GEMM & flash-attn fwd TFLOPS per B200 (% of tensor peak), 1/2/4/8 GPU"
+UNIT = "TFLOP/s"
+GEMM_N = 8192
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# DRAM bytes (read + write) of one 8192^3 GEMM launch; from the ncu capture summarised in
+# profiles/gemm_tn_kernel_bf16_8192.md.  None until a capture exists.
+GEMM_DRAM_TRAFFIC_BYTES = None
+ORACLE_TILE = (64, 64, 32)  # logical tile of the reference's GEMM example configuration
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks during the timed region (read-only NVML queries; never sets anything)
+class ClockSampler:
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+
+    def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def _reason_names(self, mask):
+        p = self._nvml
+        table = {
+            "sw_power_cap": getattr(p, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_slowdown": getattr(p, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "sw_thermal_slowdown": getattr(p, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "hw_thermal_slowdown": getattr(p, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "hw_power_brake_slowdown": getattr(p, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        return {k for k, bit in table.items() if mask & bit}
+
+    def _run(self):
+        if self._nvml is None:
+            self._run_smi()
+            return
+        p = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(p.nvmlDeviceGetClockInfo(self._h, p.NVML_CLOCK_SM))
+                try:
+                    mask = p.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    mask = p.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                self.reasons |= self._reason_names(mask)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def _run_smi(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [x.strip() for x in out.strip().split(",")]
+                self.samples.append(int(parts[0]))
+                self.max_mhz = int(parts[1])
+                for n, v in zip(names, parts[2:]):
+                    if v.lower().startswith("active"):
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.1)
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=2)
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+# ---------------------------------------------------------------------------------------------
+def cpu_oracle_gemm_sample(num_tiles: int, seed: int = 0):
+    """Times the CPU oracle (the plain-C port of the reference's generated matmul) on a seeded
+    sample of logical 64x64 output tiles of the 8192^3 problem, all host cores."""
+    import oracle
+    o = oracle.load()
+    n = GEMM_N
+    rng = np.random.default_rng(seed)
+    a = (rng.standard_normal((n, n), dtype=np.float32) / np.float32(np.sqrt(n)))
+    b = (rng.standard_normal((n, n), dtype=np.float32) / np.float32(np.sqrt(n)))
+    bm, bn, bk = ORACLE_TILE
+    ids = rng.choice((n // bm) * (n // bn), size=num_tiles, replace=False)
+    return o, a, b, ids
+
+
+def time_oracle(o, a, b, ids):
+    bm, bn, bk = ORACLE_TILE
+    t0 = time.perf_counter()
+    o.matmul_tiles(a, b, bm, bn, bk, ids)
+    dt = time.perf_counter() - t0
+    flops = 2.0 * len(ids) * bm * bn * a.shape[1]
+    return dt, flops
+
+
+def cpu_baseline(target_seconds: float = 12.0):
+    o, a, b, ids = cpu_oracle_gemm_sample(2048)
+    dt, fl = time_oracle(o, a, b, ids[:16])  # probe
+    rate = fl / dt
+    per_tile = fl / 16
+    count = int(max(16, min(len(ids), target_seconds * rate / per_tile)))
+    dt, fl = time_oracle(o, a, b, ids[:count])
+    return {
+        "value": fl / dt / 1e12, "unit": UNIT, "cores": o.num_threads(), "kind": "port",
+        "sample": f"{count} seeded logical 64x64 output tiles of the 8192^3 GEMM (k = 8192 each), "
+                  f"{dt:.1f} s; full problem by linear extrapolation {2.0 * GEMM_N ** 3 / (fl / dt):.0f} s",
+    }
+
+
+def run_reference(args, rank, world):
+    """The reference's own CPU implementation of the path (its generated C, restated in
+    oracle/sile_oracle.c; the reference itself needs a Rust toolchain that is absent)."""
+    if rank != 0:
+        return
+    tiles_per_step = 32
+    o, a, b, ids = cpu_oracle_gemm_sample(tiles_per_step * 8)
+    for w in range(args.warmup):
+        time_oracle(o, a, b, ids[:tiles_per_step])
+    total_t, total_f = 0.0, 0.0
+    for s in range(args.steps):
+        lo = (s % 8) * tiles_per_step
+        dt, fl = time_oracle(o, a, b, ids[lo:lo + tiles_per_step])
+        total_t += dt
+        total_f += fl
+    value = total_f / total_t / 1e12
+    sample = f"{tiles_per_step} seeded logical 64x64 output tiles (k = 8192) of the 8192^3 GEMM per step"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_t / max(args.steps, 1) * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "gemm_bf16_8192: M=N=K=8192 (oracle runs the bf16 values upcast to f32)",
+                   "tile": "64x64x32"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": o.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--chunks", type=int, default=4, help="M chunks used to overlap the all-gather (N > 1)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the attention / f32 side measurements")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import sile_b200 as sb
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    sb._lib.lib()  # fail loudly if the extension is missing
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}", file=sys.stderr)
+
+    n = GEMM_N
+    p = world
+    nshard = n // p
+    dev = torch.device("cuda", local_rank)
+    g = torch.Generator(device=dev).manual_seed(0)
+    a = (torch.randn(n, n, generator=g, device=dev) / n ** 0.5).to(torch.bfloat16)
+    g.manual_seed(1)
+    # column-major B: stored [N, K]; every rank draws the same B and keeps its column block
+    b_full = (torch.randn(n, n, generator=g, device=dev) / n ** 0.5).to(torch.bfloat16)
+    b_shard = b_full[rank * nshard:(rank + 1) * nshard].contiguous()
+    if p > 1:
+        del b_full
+    c = torch.zeros(n, n, device=dev, dtype=torch.bfloat16)
+    bm, bn, bk = ORACLE_TILE
+    launches_per_step = 1
+
+    if p == 1:
+        kl = sb.matmul(a, b_shard, c, bm, bn, bk, b_layout=sb._lib.LAYOUT_COL_MAJOR)
+
+        def step():
+            kl.apply()
+    else:
+        nch = max(1, args.chunks)
+        rows = n // nch
+        cs = torch.zeros(n, nshard, device=dev, dtype=torch.bfloat16)
+        gathered = [torch.empty(p, rows, nshard, device=dev, dtype=torch.bfloat16) for _ in range(nch)]
+        comm = torch.cuda.Stream(device=dev)
+        events = [torch.cuda.Event() for _ in range(nch)]
+        done = torch.cuda.Event()
+        launches_per_step = 2 * nch
+
+        def step():
+            main_stream = torch.cuda.current_stream()
+            comm.wait_stream(main_stream)
+            for i in range(nch):
+                r0 = i * rows
+                sb.matmul_shard(a[r0:r0 + rows], b_shard, cs[r0:r0 + rows], 0, nshard, bm, bn, bk)
+                events[i].record(main_stream)
+                with torch.cuda.stream(comm):
+                    comm.wait_event(events[i])
+                    dist.all_gather_into_tensor(gathered[i], cs[r0:r0 + rows])
+                    sb.unshard_columns(c[r0:r0 + rows], gathered[i], stream=comm)
+            done.record(comm)
+            main_stream.wait_event(done)
+
+    def barrier():
+        if p > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if p == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing -------------------------------------------------------------
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    # keep the GPU busy a little longer so the sampler sees the loaded clock even for short runs
+    if sampler is not None and len(sampler.samples) < 8:
+        t_end = time.time() + 0.25
+        while time.time() < t_end:
+            step()
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler is not None else None
+    barrier()
+    sb.synchronize()
+    ms_step = ms_total / args.steps
+    flops = 2.0 * n ** 3
+    value = flops / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the C ABI with host buffers ----------------------------------------
+    a_h = a.cpu().pin_memory()
+    b_h = b_shard.cpu().pin_memory()
+    c_h = torch.zeros(n, nshard, dtype=torch.bfloat16).pin_memory()
+
+    class _KN:  # B travels as its logical [K, N_shard] shape
+        shape = (n, nshard)
+
+        @staticmethod
+        def data_ptr():
+            return b_h.data_ptr()
+
+    desc = sb.make_desc(sb._lib.OP_MATMUL, sb._lib.DTYPE_BF16, sb._lib.DTYPE_BF16, sb._lib.LAYOUT_COL_MAJOR,
+                        consts=(bm, bn, bk))
+    host_launch = sb.KernelLauncher(desc, [a_h, _KN, c_h]).grid((n // bm, nshard // bn, 1))
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        host_launch.apply_host()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        host_launch.apply_host()
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0) / e2e_steps
+    e2e = {
+        "value": flops / e2e_s / 1e12, "unit": UNIT,
+        "h2d_bytes_per_step": p * (a_h.numel() + b_h.numel()) * 2,
+        "d2h_bytes_per_step": p * c_h.numel() * 2,
+        "ms_per_step": e2e_s * 1e3,
+        "api": "sile_cuda_launch_host (pinned host buffers; every rank stages A and its column block of B, "
+               "returns its column block of C)",
+    }
+    e2e_check = float((c_h[:64].float() - c[:64, rank * nshard:(rank + 1) * nshard].float().cpu()).abs().max())
+
+    # ---- side measurements (N = 1): attention forward and the f32 GEMM ----------------------------
+    extras = {}
+    peaks, peak_src = load_peaks()
+    if p == 1 and not args.no_extras:
+        def timed(fn, iters):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(iters):
+                fn()
+            s1.record()
+            torch.cuda.synchronize()
+            return s0.elapsed_time(s1) / iters
+
+        for name, (bh, s, causal) in {"attn_fwd_b4_h32_s4096_d128_noncausal": (128, 4096, False),
+                                      "attn_fwd_h32_s8192_d128_causal_one_gpu_shard": (32, 8192, True),
+                                      "attn_fwd_b8_h32_s8192_d128_causal": (256, 8192, True)}.items():
+            g.manual_seed(2)
+            q, k, v = [torch.randn(bh, s, 128, generator=g, device=dev).to(torch.bfloat16) for _ in range(3)]
+            o = torch.zeros_like(q)
+            akl = sb.attention(q, k, v, o, 1.0 / 128 ** 0.5, causal)
+            ms = timed(akl.apply, 20 if bh < 256 else 10)
+            fl = 4.0 * bh * s * s * 128 * (0.5 if causal else 1.0)
+            tf = fl / (ms * 1e-3) / 1e12
+            extras[name] = {"ms": ms, "tflops": tf, "frac_of_nominal_dense_bf16": tf / NOMINAL_BF16_TFLOPS,
+                            "frac_of_measured_gemm_peak": tf / peaks["bf16_tflops"]}
+            del q, k, v, o
+        af = torch.rand(4096, 4096, generator=g, device=dev) * 2 - 1
+        bf = torch.rand(4096, 4096, generator=g, device=dev) * 2 - 1
+        cf = torch.zeros(4096, 4096, device=dev)
+        fkl = sb.matmul(af, bf, cf, 64, 64, 32)
+        ms = timed(fkl.apply, 20)
+        extras["gemm_f32_4096"] = {"ms": ms, "tflops_f32_equivalent": 2.0 * 4096 ** 3 / (ms * 1e-3) / 1e12,
+                                   "note": "3 bf16 tensor-core passes (hi*hi + hi*lo + lo*hi), f32 accumulate"}
+        sb.synchronize()
+
+    # ---- roofline of the dominant kernel ---------------------------------------------------------
+    timed_region_s = ms_total * 1e-3
+    peak_key = "bf16_tflops_sustained" if timed_region_s > 1.0 else "bf16_tflops"
+    per_gpu_flops = flops / p
+    gemm_ms = ms_step  # one step = one GEMM pass (N = 1: exactly one launch of gemm_tn_kernel)
+    achieved = per_gpu_flops / (gemm_ms * 1e-3) / 1e12
+    roofline = {
+        "bound": "tensor", "achieved": achieved, "peak": peaks[peak_key], "unit": "TFLOP/s",
+        "frac": achieved / peaks[peak_key], "traffic": GEMM_DRAM_TRAFFIC_BYTES if p == 1 else None,
+        "peak_source": f"{peak_src} {peak_key}", "frac_of_nominal_dense_bf16": achieved / NOMINAL_BF16_TFLOPS,
+        "kernel": "gemm_tn_kernel<bf16>", "algorithmic_flops_per_launch": per_gpu_flops,
+    }
+    if p > 1:
+        roofline["note"] = "per-GPU share of the whole step (GEMM chunks + all-gather + unshard), not the kernel alone"
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": p, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "workload": "gemm_bf16_8192: M=N=K=8192, A row-major, B column-major, N(0,1)/sqrt(K) bf16, f32 accumulate, bf16 out",
+            "parallelism": f"N-sharded x{p}" + ("" if p == 1 else f", {args.chunks} M-chunks, NCCL all-gather of C overlapped with compute"),
+            "l2": "inputs (2 x 128 MiB) and output (128 MiB) exceed the 126 MB L2; no flush between steps",
+            "per_gpu_tflops": value / p,
+        },
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+        "roofline": roofline, "e2e_matches_device_result": e2e_check == 0.0,
+    }
+    if extras:
+        line["extras"] = extras
+    if rank == 0 and p == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if p > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

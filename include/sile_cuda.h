@@ -119,6 +119,24 @@ int sile_cuda_launch(const SileKernelDesc* desc, void* const* dev_buffers, const
 int sile_cuda_launch_host(const SileKernelDesc* desc, void* const* host_buffers, const int64_t* shapes,
                           int64_t num_shapes, const uint32_t grid[3]);
 
+/* ---- multi-GPU sharding ---------------------------------------------------------
+ * No counterpart in the reference (single process, single device,
+ * crates/sile-core/src/stream.rs:4-19).  A matmul splits by output-column block:
+ * the rank owning columns [n_begin, n_begin + n_count) computes
+ * C[:, n_begin : n_begin+n_count] = A * B[:, n_begin : n_begin+n_count].
+ * `b_shard` is that block of a column-major B ([n_count, K] contiguous); `c` is
+ * the base of a row-major buffer with `n_total` columns (pass n_total = n_count
+ * and n_begin = 0 for a packed shard buffer).  Asynchronous on `stream`. */
+int sile_cuda_matmul_shard(const SileKernelDesc* desc, const void* a, const void* b_shard, void* c,
+                           int64_t m, int64_t n_total, int64_t k, int64_t n_begin, int64_t n_count,
+                           void* stream);
+
+/* Lays the rank-major result of an all-gather of packed column blocks,
+ * src[parts][rows][cols], out as one row-major matrix dst[rows][parts*cols].
+ * `dtype` is a SILE_DTYPE_* giving the element size. */
+int sile_cuda_unshard_columns(void* dst, const void* src, int64_t parts, int64_t rows, int64_t cols,
+                              int32_t dtype, void* stream);
+
 /* Device selection, after Device::cuda(index) (crates/sile-core/src/device.rs:23-35).
  * Fails with SILE_ERR_NO_DEVICE when the index does not name an sm_100 GPU. */
 int sile_cuda_set_device(int index);

@@ -158,3 +158,28 @@ def synchronize(stream=None) -> None:
     if stream is None:
         stream = torch.cuda.current_stream()
     _check(_lib.lib().sile_cuda_synchronize(C.c_void_p(stream.cuda_stream)))
+
+
+def _stream_handle(stream):
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return C.c_void_p(stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream))
+
+
+def matmul_shard(a, b_shard, c, n_begin: int, n_total: int, bm=1, bn=1, bk=1, stream=None) -> None:
+    """One rank's column block of a sharded matmul: ``c[:, n_begin:n_begin+n_count] = a @ B_block``.
+
+    ``b_shard`` is the [n_count, K] block of a column-major B; ``c`` is the base of a row-major
+    buffer with ``n_total`` columns (``n_total == n_count`` for a packed shard buffer)."""
+    desc = make_desc(OP_MATMUL, _dtype_code(a), _dtype_code(c), LAYOUT_COL_MAJOR, consts=(bm, bn, bk))
+    m, k = a.shape
+    _check(_lib.lib().sile_cuda_matmul_shard(C.byref(desc), a.data_ptr(), b_shard.data_ptr(), c.data_ptr(),
+                                             m, n_total, k, n_begin, b_shard.shape[0], _stream_handle(stream)))
+
+
+def unshard_columns(dst, src, stream=None) -> None:
+    """``dst[r, j*cols + c] = src[j, r, c]`` for the gathered ``src`` of shape [parts, rows, cols]."""
+    parts, rows, cols = src.shape
+    _check(_lib.lib().sile_cuda_unshard_columns(dst.data_ptr(), src.data_ptr(), parts, rows, cols,
+                                                _dtype_code(src), _stream_handle(stream)))

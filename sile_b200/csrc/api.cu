@@ -132,7 +132,7 @@ struct ArgSpan {
 };
 
 // Validates shapes for `desc` and lists the byte size / direction of every buffer.
-int describe_args(const SileKernelDesc* d, const int64_t* shapes, int64_t ns, std::vector<ArgSpan>* out) {
+int describe_args(const SileKernelDesc* d, const int64_t* shapes, int64_t ns, int64_t ntg, std::vector<ArgSpan>* out) {
   out->clear();
   const size_t in_sz = dtype_size(d->in_dtype), out_sz = dtype_size(d->out_dtype);
   auto pos = [&](int64_t v) { return v > 0; };
@@ -146,7 +146,11 @@ int describe_args(const SileKernelDesc* d, const int64_t* shapes, int64_t ns, st
                     (long long)shapes[1], (long long)shapes[2], (long long)shapes[3], (long long)shapes[4], (long long)shapes[5]);
       out->push_back({static_cast<size_t>(m * k) * in_sz, true, false});
       out->push_back({static_cast<size_t>(k * n) * in_sz, true, false});
-      out->push_back({static_cast<size_t>(m * n) * out_sz, true, true});  // untouched tiles must survive the round trip
+      // C travels to the device only when part of it will not be written (ragged logical
+      // tiles or a short grid): untouched elements must survive the round trip.
+      const int64_t bm = const_or_one(d, 0), bn = const_or_one(d, 1);
+      const bool partial = (m % bm) || (n % bn) || (ntg < (m / bm) * (n / bn));
+      out->push_back({static_cast<size_t>(m * n) * out_sz, partial, true});
       return SILE_OK;
     }
     case SILE_OP_ATTENTION: {
@@ -307,7 +311,18 @@ int launch_host(const SileKernelDesc* d, void* const* host, const int64_t* shape
   if (int rc = check_device()) return rc;
   if (!host || !shapes) return fail(SILE_ERR_INVALID, "null argument");
   std::vector<ArgSpan> args;
-  if (int rc = describe_args(d, shapes, ns, &args)) return rc;
+  if (int rc = describe_args(d, shapes, ns, ntg, &args)) return rc;
+  static thread_local int pool_dev = -1;
+  int cur_dev = 0;
+  SILE_CUDA_TRY(cudaGetDevice(&cur_dev));
+  if (pool_dev != cur_dev) {
+    // keep freed staging buffers in the stream-ordered pool between calls
+    cudaMemPool_t pool;
+    SILE_CUDA_TRY(cudaDeviceGetDefaultMemPool(&pool, cur_dev));
+    uint64_t keep = UINT64_MAX;
+    SILE_CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+    pool_dev = cur_dev;
+  }
   cudaStream_t stream = nullptr;
   SILE_CUDA_TRY(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
   std::vector<void*> dev(args.size(), nullptr);
@@ -424,7 +439,7 @@ int sile_cuda_launch(const SileKernelDesc* desc, void* const* dev_buffers, const
   if (int rc = check_device()) return rc;
   if (!dev_buffers || !shapes || !grid) return fail(SILE_ERR_INVALID, "null argument");
   std::vector<ArgSpan> args;
-  if (int rc = describe_args(desc, shapes, num_shapes, &args)) return rc;
+  if (int rc = describe_args(desc, shapes, num_shapes, grid_product(grid), &args)) return rc;
   for (size_t i = 0; i < args.size(); ++i)
     if (!dev_buffers[i]) return fail(SILE_ERR_INVALID, "null buffer %zu", i);
   const int rc = launch_device(desc, dev_buffers, shapes, num_shapes, grid_product(grid), static_cast<cudaStream_t>(stream));
@@ -436,6 +451,33 @@ int sile_cuda_launch_host(const SileKernelDesc* desc, void* const* host_buffers,
                           const uint32_t grid[3]) {
   if (!grid) return fail(SILE_ERR_INVALID, "null argument");
   return launch_host(desc, host_buffers, shapes, num_shapes, grid_product(grid));
+}
+
+int sile_cuda_matmul_shard(const SileKernelDesc* desc, const void* a, const void* b_shard, void* c, int64_t m, int64_t n_total,
+                           int64_t k, int64_t n_begin, int64_t n_count, void* stream) {
+  if (int rc = validate_desc(desc)) return rc;
+  if (int rc = check_device()) return rc;
+  if (desc->op != SILE_OP_MATMUL) return fail(SILE_ERR_INVALID, "matmul_shard: description is not a matmul");
+  if (!a || !b_shard || !c) return fail(SILE_ERR_INVALID, "null buffer");
+  if (n_begin < 0 || n_count <= 0 || n_begin + n_count > n_total) return fail(SILE_ERR_INVALID, "matmul_shard: column block out of range");
+  if (desc->in_dtype == SILE_DTYPE_F32 || desc->b_layout != SILE_LAYOUT_COL_MAJOR)
+    return fail(SILE_ERR_UNSUPPORTED, "matmul_shard: 16-bit operands with column-major B only (a column block of B must be contiguous)");
+  GemmProblem p;
+  p.a = a; p.b = b_shard;
+  p.c = static_cast<char*>(c) + static_cast<size_t>(n_begin) * dtype_size(desc->out_dtype);
+  p.m = m; p.n = n_count; p.k = k; p.ldc = n_total;
+  p.in_dtype = desc->in_dtype; p.out_dtype = desc->out_dtype; p.b_layout = desc->b_layout;
+  p.bm = const_or_one(desc, 0); p.bn = const_or_one(desc, 1); p.bk = const_or_one(desc, 2);
+  const int rc = gemm_launch(p, static_cast<cudaStream_t>(stream));
+  if (rc == SILE_OK) t_last_status = SILE_OK;
+  return rc;
+}
+
+int sile_cuda_unshard_columns(void* dst, const void* src, int64_t parts, int64_t rows, int64_t cols, int32_t dtype, void* stream) {
+  if (int rc = check_device()) return rc;
+  const int rc = unshard_columns_launch(dst, src, parts, rows, cols, static_cast<int>(dtype_size(dtype)), static_cast<cudaStream_t>(stream));
+  if (rc == SILE_OK) t_last_status = SILE_OK;
+  return rc;
 }
 
 void sile_kernel_matmul(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {

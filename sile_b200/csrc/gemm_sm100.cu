@@ -422,7 +422,8 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
   GemmParams gp{};
   gp.m_valid = static_cast<int>(e.m_valid);
   gp.n_valid = static_cast<int>(e.n_valid);
-  gp.ldc = p.n;
+  gp.ldc = p.ldc > 0 ? p.ldc : p.n;
+  if (gp.ldc < p.n) return fail(SILE_ERR_INVALID, "matmul: ldc smaller than N");
   gp.m_blocks = static_cast<int>((e.m_valid + kBM - 1) / kBM);
   gp.n_blocks = static_cast<int>((e.n_valid + kBN - 1) / kBN);
   gp.lbm = static_cast<int>(bm);
@@ -512,7 +513,7 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
   const int grid = std::min(num_tiles, sms);
 
   const size_t out_elt = p.out_dtype == SILE_DTYPE_F32 ? 4 : 2;
-  const int vec_ok = (reinterpret_cast<uintptr_t>(p.c) % 16 == 0) && ((p.n * out_elt) % 16 == 0);
+  const int vec_ok = (reinterpret_cast<uintptr_t>(p.c) % 16 == 0) && ((gp.ldc * out_elt) % 16 == 0);
   switch (p.out_dtype) {
     case SILE_DTYPE_F32: return launch_typed<float>(ta, tb, p.c, gp, idesc, vec_ok, status, grid, stream);
     case SILE_DTYPE_BF16: return launch_typed<__nv_bfloat16>(ta, tb, p.c, gp, idesc, vec_ok, status, grid, stream);

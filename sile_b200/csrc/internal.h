@@ -37,6 +37,7 @@ struct GemmProblem {
   const void* b = nullptr;   // f32: [K,N] row-major; 16-bit: per b_layout
   void* c = nullptr;         // [M,N] row-major
   int64_t m = 0, n = 0, k = 0;
+  int64_t ldc = 0;           // elements between rows of C; 0 = n
   int in_dtype = SILE_DTYPE_F32;
   int out_dtype = SILE_DTYPE_F32;
   int b_layout = SILE_LAYOUT_ROW_MAJOR;
@@ -49,6 +50,11 @@ struct GemmProblem {
 };
 size_t gemm_workspace_bytes(const GemmProblem& p);
 int gemm_launch(const GemmProblem& p, cudaStream_t stream);
+
+// dst[r, j*cols + c] = src[j, r, c]: lays the rank-major result of an all-gather of column
+// blocks out as one row-major matrix.
+int unshard_columns_launch(void* dst, const void* src, int64_t parts, int64_t rows, int64_t cols, int elt_size,
+                           cudaStream_t stream);
 
 // ---- attention forward ----------------------------------------------------------
 struct AttnProblem {

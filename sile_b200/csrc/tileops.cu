@@ -190,9 +190,36 @@ __global__ void matvec_kernel(const float* __restrict__ x, const float* __restri
   }
 }
 
+// dst[r][j*cols + c] = src[j][r][c], 16 bytes per thread per step.
+__global__ void unshard_columns_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int parts, int64_t rows, int cols16) {
+  const int64_t per_part = rows * cols16;
+  const int64_t total = per_part * parts;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t j = i / per_part;
+    const int64_t rem = i - j * per_part;
+    const int64_t r = rem / cols16;
+    const int64_t c = rem - r * cols16;
+    __stcs(dst + (r * parts + j) * cols16 + c, __ldcs(src + i));
+  }
+}
+
 bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
 }  // namespace
+
+int unshard_columns_launch(void* dst, const void* src, int64_t parts, int64_t rows, int64_t cols, int elt_size,
+                           cudaStream_t stream) {
+  if (parts <= 0 || rows <= 0 || cols <= 0) return SILE_OK;
+  if (!dst || !src) return fail(SILE_ERR_INVALID, "unshard: null buffer");
+  if ((cols * elt_size) % 16 != 0 || !aligned16(dst) || !aligned16(src))
+    return fail(SILE_ERR_UNSUPPORTED, "unshard: column blocks must be multiples of 16 bytes and 16-byte aligned");
+  const int64_t cols16 = cols * elt_size / 16;
+  unshard_columns_kernel<<<grid_for(parts * rows * cols16, 8), kThreads, 0, stream>>>(
+      static_cast<uint4*>(dst), static_cast<const uint4*>(src), static_cast<int>(parts), rows, static_cast<int>(cols16));
+  SILE_CUDA_TRY(cudaGetLastError());
+  return SILE_OK;
+}
 
 int vec_add_launch(const float* a, const float* b, float* c, int64_t n, cudaStream_t stream) {
   if (n <= 0) return SILE_OK;
