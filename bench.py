@@ -36,6 +36,13 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # profiles/gemm_tn_kernel_bf16_8192.md.  None until a capture exists.
 GEMM_DRAM_TRAFFIC_BYTES = None
 ORACLE_TILE = (64, 64, 32)  # logical tile of the reference's GEMM example configuration
+# name -> (batch*heads, seq, causal) for attention; None for the f32 GEMM
+SIDE_WORKLOADS = {
+    "attn_fwd_b4_h32_s4096_d128_noncausal": (128, 4096, False),
+    "attn_fwd_h32_s8192_d128_causal_one_gpu_shard": (32, 8192, True),
+    "attn_fwd_b8_h32_s8192_d128_causal": (256, 8192, True),
+    "gemm_f32_4096": None,
+}
 
 
 def load_peaks():
@@ -196,6 +203,44 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_side_workload(name, iters, warmup, peaks):
+    """Times one side workload on the current device with CUDA events; returns its result dict."""
+    import torch
+    import sile_b200 as sb
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(2)
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(iters):
+            fn()
+        s1.record()
+        torch.cuda.synchronize()
+        sb.synchronize()
+        return s0.elapsed_time(s1) / iters
+
+    spec = SIDE_WORKLOADS[name]
+    if spec is None:
+        af = torch.rand(4096, 4096, generator=g, device=dev) * 2 - 1
+        bf = torch.rand(4096, 4096, generator=g, device=dev) * 2 - 1
+        cf = torch.zeros(4096, 4096, device=dev)
+        ms = timed(sb.matmul(af, bf, cf, 64, 64, 32).apply)
+        return {"ms": ms, "tflops_f32_equivalent": 2.0 * 4096 ** 3 / (ms * 1e-3) / 1e12,
+                "note": "3 bf16 tensor-core passes (hi*hi + hi*lo + lo*hi), f32 accumulate"}
+    bh, s, causal = spec
+    q, k, v = [torch.randn(bh, s, 128, generator=g, device=dev).to(torch.bfloat16) for _ in range(3)]
+    o = torch.zeros_like(q)
+    ms = timed(sb.attention(q, k, v, o, 1.0 / 128 ** 0.5, causal).apply)
+    fl = 4.0 * bh * s * s * 128 * (0.5 if causal else 1.0)
+    tf = fl / (ms * 1e-3) / 1e12
+    return {"ms": ms, "tflops": tf, "frac_of_nominal_dense_bf16": tf / NOMINAL_BF16_TFLOPS,
+            "frac_of_measured_gemm_peak": tf / peaks["bf16_tflops"]}
+
+
 # ---------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -206,6 +251,9 @@ def main():
     ap.add_argument("--chunks", type=int, default=4, help="M chunks used to overlap the all-gather (N > 1)")
     ap.add_argument("--no-extras", action="store_true", help="skip the attention / f32 side measurements")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="gemm_bf16_8192", choices=["gemm_bf16_8192"] + sorted(SIDE_WORKLOADS),
+                    help="gemm_bf16_8192 is the headline bench; the others time one side workload on one GPU "
+                         "(used for profiling) and print a short JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -228,6 +276,13 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if args.workload != "gemm_bf16_8192":
+        if rank == 0:
+            peaks, _ = load_peaks()
+            res = run_side_workload(args.workload, args.steps, args.warmup, peaks)
+            res.update({"workload": args.workload, "steps": args.steps, "warmup": args.warmup})
+            print(json.dumps(res), flush=True)
+        return
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}", file=sys.stderr)
 
@@ -352,39 +407,8 @@ def main():
     extras = {}
     peaks, peak_src = load_peaks()
     if p == 1 and not args.no_extras:
-        def timed(fn, iters):
-            for _ in range(3):
-                fn()
-            torch.cuda.synchronize()
-            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s0.record()
-            for _ in range(iters):
-                fn()
-            s1.record()
-            torch.cuda.synchronize()
-            return s0.elapsed_time(s1) / iters
-
-        for name, (bh, s, causal) in {"attn_fwd_b4_h32_s4096_d128_noncausal": (128, 4096, False),
-                                      "attn_fwd_h32_s8192_d128_causal_one_gpu_shard": (32, 8192, True),
-                                      "attn_fwd_b8_h32_s8192_d128_causal": (256, 8192, True)}.items():
-            g.manual_seed(2)
-            q, k, v = [torch.randn(bh, s, 128, generator=g, device=dev).to(torch.bfloat16) for _ in range(3)]
-            o = torch.zeros_like(q)
-            akl = sb.attention(q, k, v, o, 1.0 / 128 ** 0.5, causal)
-            ms = timed(akl.apply, 20 if bh < 256 else 10)
-            fl = 4.0 * bh * s * s * 128 * (0.5 if causal else 1.0)
-            tf = fl / (ms * 1e-3) / 1e12
-            extras[name] = {"ms": ms, "tflops": tf, "frac_of_nominal_dense_bf16": tf / NOMINAL_BF16_TFLOPS,
-                            "frac_of_measured_gemm_peak": tf / peaks["bf16_tflops"]}
-            del q, k, v, o
-        af = torch.rand(4096, 4096, generator=g, device=dev) * 2 - 1
-        bf = torch.rand(4096, 4096, generator=g, device=dev) * 2 - 1
-        cf = torch.zeros(4096, 4096, device=dev)
-        fkl = sb.matmul(af, bf, cf, 64, 64, 32)
-        ms = timed(fkl.apply, 20)
-        extras["gemm_f32_4096"] = {"ms": ms, "tflops_f32_equivalent": 2.0 * 4096 ** 3 / (ms * 1e-3) / 1e12,
-                                   "note": "3 bf16 tensor-core passes (hi*hi + hi*lo + lo*hi), f32 accumulate"}
-        sb.synchronize()
+        for name in SIDE_WORKLOADS:
+            extras[name] = run_side_workload(name, 10 if "b8" in name else 20, 3, peaks)
 
     # ---- roofline of the dominant kernel ---------------------------------------------------------
     timed_region_s = ms_total * 1e-3
