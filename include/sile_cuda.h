@@ -137,6 +137,39 @@ int sile_cuda_matmul_shard(const SileKernelDesc* desc, const void* a, const void
 int sile_cuda_unshard_columns(void* dst, const void* src, int64_t parts, int64_t rows, int64_t cols,
                               int32_t dtype, void* stream);
 
+/* ---- f32 matmul that allocates nothing -------------------------------------------
+ * Has no counterpart in the reference.  For callers that cannot let a library
+ * allocate device memory -- a process whose own arena already owns all of HBM, a
+ * latency-critical loop that must stay clear of the driver's allocation lock and
+ * the device-wide synchronisation an allocation can imply, or a deployment that
+ * forbids allocation after start-up.  Same result as an f32 SILE_OP_MATMUL through
+ * sile_cuda_launch with the full logical grid: C[M,N] = A[M,K] * B[K,N], all
+ * row-major f32 DEVICE buffers, logical tile (bm, bn, bk) deciding which part of C
+ * is written (0 = 1).
+ *
+ * The bf16 split planes the kernel needs live in a 32 MiB array that is part of
+ * the library image (every GPU that loads the library holds those 32 MiB until
+ * the process exits), so the problem must satisfy
+ *     4 * (M + N) * roundup(K, 64) bytes <= 32 MiB
+ * (e.g. M = N = 1024 with K = 4096, or M = N = 2048 with K = 2048); anything larger
+ * is rejected with SILE_ERR_UNSUPPORTED and a message naming the size.  The call
+ * makes no cudaMalloc / cudaFree / stream-ordered allocation, here or in anything
+ * it calls.
+ *
+ * The first call on each device resolves the array's device address and sets a
+ * kernel attribute; make that first call before any stream capture begins.
+ * All calls on a device share the one array: it still holds the previous call's
+ * planes when the next call starts (every plane element is rewritten before it is
+ * read), and two calls whose kernels can overlap on the GPU -- different streams,
+ * or different host threads -- race on it.  Serialise them on one stream.
+ *
+ * Asynchronous on `stream` when `wait` is 0.  With `wait` != 0 the call returns
+ * after the stream has drained and reports SILE_ERR_TIMEOUT if a bounded
+ * device-side wait ran out during this (or an earlier non-waiting) call. */
+int sile_cuda_matmul_f32_noalloc(const float* a, const float* b, float* c, int64_t m, int64_t n,
+                                 int64_t k, int64_t bm, int64_t bn, int64_t bk, void* stream,
+                                 int32_t wait);
+
 /* Device selection, after Device::cuda(index) (crates/sile-core/src/device.rs:23-35).
  * Fails with SILE_ERR_NO_DEVICE when the index does not name an sm_100 GPU. */
 int sile_cuda_set_device(int index);

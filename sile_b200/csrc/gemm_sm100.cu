@@ -23,6 +23,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <mutex>
 #include <type_traits>
 
 #include "internal.h"
@@ -522,3 +523,148 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
 }
 
 }  // namespace sile
+
+// ---- f32 matmul without any allocation ------------------------------------------------
+// Some hosts cannot let a library allocate device memory: a serving process that has handed
+// all of HBM to its own arena (a cudaMalloc there fails, or fragments the arena's neighbour),
+// a control loop that must not take the driver's allocation lock or its implicit device-wide
+// synchronisation, a deployment whose policy forbids allocation after start-up.  For them the
+// scratch of the f32 split lives in a fixed array inside the library image and the time-out
+// status word beside it; nothing below calls cudaMalloc, cudaMallocAsync, cudaFree or any
+// allocating library routine.
+//
+// The array's name is only a host-side handle for the symbol: host code must never pass it to
+// a kernel.  The device address is looked up with cudaGetSymbolAddress once per device, with
+// that device current, and the kernels receive that pointer.
+namespace sile {
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = size_t(32) << 20;  // 32 MiB per GPU that loads the library
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+static __device__ int g_noalloc_status;
+
+struct NoAllocDevice {
+  void* scratch = nullptr;
+  int* status = nullptr;
+};
+NoAllocDevice g_noalloc_dev[64];
+std::mutex g_noalloc_mutex;
+
+// First use on a device: resolves the device addresses of the two symbols and raises the
+// kernel's dynamic shared-memory limit.  Must run outside stream capture.
+int noalloc_setup(int dev, NoAllocDevice* out) {
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  NoAllocDevice& d = g_noalloc_dev[dev];
+  if (!d.scratch) {
+    void* scratch = nullptr;
+    void* status = nullptr;
+    SILE_CUDA_TRY(cudaGetSymbolAddress(&scratch, g_noalloc_scratch));
+    SILE_CUDA_TRY(cudaGetSymbolAddress(&status, g_noalloc_status));
+    SILE_CUDA_TRY(cudaFuncSetAttribute(gemm_tn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    d.scratch = scratch;
+    d.status = static_cast<int*>(status);
+  }
+  *out = d;
+  return SILE_OK;
+}
+
+}  // namespace
+}  // namespace sile
+
+extern "C" int sile_cuda_matmul_f32_noalloc(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                                            int64_t bm, int64_t bn, int64_t bk, void* stream_handle, int32_t wait) {
+  using namespace sile;
+  if (!a || !b || !c) return fail(SILE_ERR_INVALID, "matmul_f32_noalloc: null buffer");
+  if (m <= 0 || n <= 0 || k <= 0) return fail(SILE_ERR_INVALID, "matmul_f32_noalloc: non-positive dimension");
+  if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) return fail(SILE_ERR_INVALID, "matmul_f32_noalloc: dimension too large");
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(SILE_ERR_NO_DEVICE, "matmul_f32_noalloc: no CUDA device");
+  }
+  int major = 0;
+  SILE_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (major != 10 || dev < 0 || dev >= 64) return fail(SILE_ERR_NO_DEVICE, "matmul_f32_noalloc: device %d is not a usable sm_100 GPU", dev);
+
+  GemmProblem p;
+  p.a = a; p.b = b; p.c = c;
+  p.m = m; p.n = n; p.k = k;
+  p.bm = bm > 0 ? bm : 1; p.bn = bn > 0 ? bn : 1; p.bk = bk > 0 ? bk : 1;
+  const EffectiveDims e = effective_dims(p);
+  const size_t need = static_cast<size_t>(2 * (m + n) * e.kp) * sizeof(__nv_bfloat16);
+  if (need > kNoAllocScratchBytes)
+    return fail(SILE_ERR_UNSUPPORTED,
+                "matmul_f32_noalloc: this problem needs %zu bytes of scratch (4 * (M + N) * K rounded up to 64); the built-in "
+                "array holds %zu bytes -- use sile_cuda_launch for larger problems", need, kNoAllocScratchBytes);
+  if (e.m_valid == 0 || e.n_valid == 0) return SILE_OK;  // no whole logical tile
+
+  NoAllocDevice nd;
+  if (int rc = noalloc_setup(dev, &nd)) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+
+  // Planes A_hi | A_lo ([2M, Kp]) then B^T_hi | B^T_lo ([2N, Kp]).  Both split kernels write
+  // every element of their planes, zero padding included, so nothing left over from an earlier
+  // call is ever read.
+  auto* a_hi = static_cast<__nv_bfloat16*>(nd.scratch);
+  __nv_bfloat16* a_lo = a_hi + m * e.kp;
+  __nv_bfloat16* b_hi = a_lo + m * e.kp;
+  __nv_bfloat16* b_lo = b_hi + n * e.kp;
+  {
+    const int64_t total = m * (e.kp >> 3);
+    const int threads = 256;
+    const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
+    const int vec4 = (k % 4 == 0) && (reinterpret_cast<uintptr_t>(a) % 16 == 0);
+    split_rows_kernel<<<blocks, threads, 0, stream>>>(a, k, a_hi, a_lo, static_cast<int>(m), static_cast<int>(e.k_eff),
+                                                      static_cast<int>(e.kp), vec4);
+    SILE_CUDA_TRY(cudaGetLastError());
+    dim3 grid(static_cast<unsigned>((n + 31) / 32), static_cast<unsigned>(e.kp / 64));
+    split_transpose_kernel<<<grid, dim3(32, 8), 0, stream>>>(b, n, b_hi, b_lo, static_cast<int>(n), static_cast<int>(e.k_eff),
+                                                             static_cast<int>(e.kp));
+    SILE_CUDA_TRY(cudaGetLastError());
+  }
+
+  CUtensorMap ta, tb;
+  const uint32_t box_a[2] = {kBK, kBM};
+  const uint32_t box_b[2] = {kBK, kBN};
+  const uint64_t dims_a[2] = {static_cast<uint64_t>(e.kp), static_cast<uint64_t>(2 * m)};
+  const uint64_t dims_b[2] = {static_cast<uint64_t>(e.kp), static_cast<uint64_t>(2 * n)};
+  const uint64_t stride[1] = {static_cast<uint64_t>(e.kp) * 2};
+  if (int rc = encode_tensor_map(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_hi, dims_a, stride, box_a, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = encode_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_hi, dims_b, stride, box_b, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+
+  GemmParams gp{};
+  gp.m_valid = static_cast<int>(e.m_valid);
+  gp.n_valid = static_cast<int>(e.n_valid);
+  gp.ldc = n;
+  gp.m_blocks = static_cast<int>((e.m_valid + kBM - 1) / kBM);
+  gp.n_blocks = static_cast<int>((e.n_valid + kBN - 1) / kBN);
+  gp.lbm = static_cast<int>(p.bm);
+  gp.lbn = static_cast<int>(p.bn);
+  gp.ltiles_n = static_cast<int>(n / p.bn);
+  gp.ntg = INT64_MAX;
+  gp.masked = 0;
+  gp.num_segs = 3;
+  gp.k_blocks_per_seg = static_cast<int>(e.kp / kBK);
+  gp.a_seg_row[0] = static_cast<int>(m); gp.b_seg_row[0] = 0;
+  gp.a_seg_row[1] = 0;                   gp.b_seg_row[1] = static_cast<int>(n);
+  gp.a_seg_row[2] = 0;                   gp.b_seg_row[2] = 0;
+
+  int sms = 148;
+  SILE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int grid = std::min(gp.m_blocks * gp.n_blocks, sms);
+  const int vec_ok = (reinterpret_cast<uintptr_t>(c) % 16 == 0) && ((n * 4) % 16 == 0);
+  const uint32_t idesc = make_idesc_f16(kBM, kBN, true, false, false);
+  gemm_tn_kernel<float><<<grid, kNumThreads, kSmemBytes, stream>>>(ta, tb, c, gp, idesc, vec_ok, nd.status);
+  SILE_CUDA_TRY(cudaGetLastError());
+
+  if (wait) {
+    SILE_CUDA_TRY(cudaStreamSynchronize(stream));
+    int st = 0;
+    SILE_CUDA_TRY(cudaMemcpy(&st, nd.status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (st != 0) {
+      SILE_CUDA_TRY(cudaMemset(nd.status, 0, sizeof(int)));
+      return fail(st, "matmul_f32_noalloc: a device-side wait ran out (code %d); the result is invalid", st);
+    }
+  }
+  return SILE_OK;
+}
