@@ -301,7 +301,8 @@ int read_and_clear_status() {
   SILE_CUDA_TRY(cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost));
   if (v != 0) {
     SILE_CUDA_TRY(cudaMemset(word, 0, sizeof(int)));
-    return fail(v, "a device-side wait ran out (code %d); results of the affected launch are invalid", v);
+    return fail(v & 0xff, "a device-side wait ran out (code %d, stuck wait sites 0x%x); results of the affected launch are invalid",
+                v & 0xff, static_cast<unsigned>(v) >> 8);
   }
   return SILE_OK;
 }

@@ -90,9 +90,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
 
-  // heavy (late) query blocks first so the causal tail is short
-  const int bh = blockIdx.x % p.bh;
-  const int qblk = p.num_qblocks - 1 - blockIdx.x / p.bh;
+  // Block order: heads are taken in groups of kHeadGroup; inside a group the late query blocks
+  // (heavy under a causal mask) of every head come first.  Concurrently resident CTAs then share
+  // the K/V of a few heads in L2, and the blocks that finish last are the light ones.
+  constexpr int kHeadGroup = 8;
+  const int group = blockIdx.x / (kHeadGroup * p.num_qblocks);
+  const int in_group = blockIdx.x - group * kHeadGroup * p.num_qblocks;
+  const int heads_here = min(kHeadGroup, p.bh - group * kHeadGroup);
+  const int bh = group * kHeadGroup + in_group % heads_here;
+  const int qblk = p.num_qblocks - 1 - in_group / heads_here;
   const int q_base = qblk * kBlockQ;
   const int n_kv[2] = {kv_blocks_for_tile(p, q_base), kv_blocks_for_tile(p, q_base + kTileQ)};
   const int n_max = max(n_kv[0], n_kv[1]);

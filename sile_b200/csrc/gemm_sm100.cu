@@ -23,6 +23,8 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <type_traits>
 
@@ -60,13 +62,15 @@ struct GemmParams {
   int lbm, lbn, ltiles_n;
   long long ntg;
   int masked;  // 1 if the logical launch mask can exclude anything
+  int group_m;  // 128-row blocks per raster group
 };
 
 __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& m_blk, int& n_blk) {
-  const int group_size = kGroupM * p.n_blocks;
+  const int group_m = p.group_m;
+  const int group_size = group_m * p.n_blocks;
   const int group = t / group_size;
-  const int first_m = group * kGroupM;
-  const int gm = min(p.m_blocks - first_m, kGroupM);
+  const int first_m = group * group_m;
+  const int gm = min(p.m_blocks - first_m, group_m);
   const int r = t - group * group_size;
   m_blk = first_m + r % gm;
   n_blk = r / gm;
@@ -267,6 +271,364 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   }
 }
 
+// ---- CTA-pair variant ---------------------------------------------------------------
+// Two CTAs of a cluster share one 256 x 256 x 64 tile: CTA r stages rows [128r, 128r+128) of A
+// and rows [128r, 128r+128) of the B tile (16 KiB + 16 KiB per stage, 6 stages), the leader
+// (cluster rank 0) issues tcgen05.mma.cta_group::2 with M = 256, N = 256 and each CTA's TMEM
+// receives its 128 accumulator rows.  Every TMA load completes on the LEADER's full barrier;
+// the leader's commits release the stage, and publish the accumulator, in both CTAs; both
+// CTAs' epilogue warps report to the leader's tmem_empty barrier.  No load is multicast.
+constexpr int kPairStages = 6;
+constexpr int kPairABytes = 128 * kBK * 2;
+constexpr int kPairBBytes = 128 * kBK * 2;
+constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 256 + 1024;
+constexpr int kPairBM = 256;
+
+__device__ __forceinline__ void pair_tile_coords(int t, const GemmParams& p, int m_blocks, int& m_blk, int& n_blk) {
+  const int kGroup = max(p.group_m / 2, 1);
+  const int group_size = kGroup * p.n_blocks;
+  const int group = t / group_size;
+  const int first_m = group * kGroup;
+  const int gm = min(m_blocks - first_m, kGroup);
+  const int r = t - group * group_size;
+  m_blk = first_m + r % gm;
+  n_blk = r / gm;
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, OutT* __restrict__ c,
+                    const GemmParams p, const uint32_t idesc, const int vec_ok, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);
+  uint64_t* empty_bar = full_bar + kPairStages;
+  uint64_t* tmem_full_bar = empty_bar + kPairStages;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tma_a);
+    prefetch_tensormap(&tma_b);
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], 8);  // 4 epilogue warps in each of the two CTAs
+    }
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(tmem_slot, kTmemCols);
+    tmem_relinquish<2>();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything is signalled across CTAs
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  const int m_blocks = (p.m_valid + kPairBM - 1) / kPairBM;
+  const int num_tiles = m_blocks * p.n_blocks;
+  const int num_kb = p.k_blocks_per_seg * p.num_segs;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        int m_blk, n_blk;
+        pair_tile_coords(t, p, m_blocks, m_blk, n_blk);
+        const int a_row = m_blk * kPairBM + static_cast<int>(rank) * 128;
+        const int b_row = n_blk * kBN + static_cast<int>(rank) * 128;
+        int seg = 0, kb_in_seg = 0;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait<true>(&empty_bar[stage], phase ^ 1u, status, SILE_ERR_TIMEOUT, 1 + 4 * rank)) { ok = false; break; }
+          uint8_t* sa = smem + stage * kPairStageBytes;
+          uint8_t* sb = sa + kPairABytes;
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * kPairStageBytes);
+          tma_load_2d_pair(sa, &tma_a, &full_bar[stage], 0, kb_in_seg * kBK, p.a_seg_row[seg] + a_row);
+          tma_load_2d_pair(sb, &tma_b, &full_bar[stage], 0, kb_in_seg * kBK, p.b_seg_row[seg] + b_row);
+          if (++kb_in_seg == p.k_blocks_per_seg) { kb_in_seg = 0; ++seg; }
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait<true>(&tmem_empty_bar[buf], acc_phase ^ 1u, status, SILE_ERR_TIMEOUT, 2)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * kBN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait<true>(&full_bar[stage], phase, status, SILE_ERR_TIMEOUT, 3)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
+          const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(sa + kPairABytes, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) umma_ss_f16<2>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair_to(&empty_bar[stage], 0);
+          umma_commit_pair_to(&empty_bar[stage], 1);
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) {
+          umma_commit_pair_to(&tmem_full_bar[buf], 0);
+          umma_commit_pair_to(&tmem_full_bar[buf], 1);
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (both CTAs) ----------------
+    const int quarter = warp & 3;
+    int it = 0;
+    bool ok = true;
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+      int m_blk, n_blk;
+      pair_tile_coords(t, p, m_blocks, m_blk, n_blk);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait<true>(&tmem_full_bar[buf], acc_phase, status, SILE_ERR_TIMEOUT, 4 + 4 * rank)) { ok = false; }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row0 = m_blk * kPairBM + static_cast<int>(rank) * 128;
+      const int row = row0 + quarter * 32 + lane;
+      const int col_base = n_blk * kBN;
+      const bool tile_fast = vec_ok && !p.masked && (row0 + 128 <= p.m_valid) && (col_base + kBN <= p.n_valid);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
+#pragma unroll 1
+      for (int ch = 0; ch < kBN / 32; ++ch) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + ch * 32, r);
+        tcgen05_wait_ld();
+        if (tile_fast || col_base + ch * 32 < p.n_valid) store_chunk<OutT>(c, p, row, col_base + ch * 32, r, tile_fast);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(&tmem_empty_bar[buf], 0);
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still touch its shared memory or TMEM
+  if (warp == 1) {
+    tcgen05_fence_after();
+    if (*reinterpret_cast<volatile int*>(status) != 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) {
+      }
+    }
+    tmem_dealloc<2>(tmem_base, kTmemCols);
+  }
+}
+
+// ---- wide CTA-pair variant -----------------------------------------------------------
+// Same pairing, but one pair owns a 256 x 512 tile: per 64-wide k block each CTA stages its 128
+// rows of A once and its 128-row shares of TWO 256-column B halves (48 KiB per stage, 4 stages),
+// and the leader issues the k block's MMAs twice, once per half, into TMEM columns [0,256) and
+// [256,512).  A is fetched from L2 once per 512 output columns instead of once per 256, which
+// cuts L2 -> shared-memory traffic per flop by a quarter.  All 512 TMEM columns hold one tile, so
+// the epilogue is not overlapped with the next tile's main loop (a few per cent of a tile once
+// K reaches the thousands).  Eight epilogue warps: four per accumulator half.
+constexpr int kWideStages = 4;
+constexpr int kWideStageBytes = kPairABytes + 2 * kPairBBytes;
+constexpr int kWideSmemBytes = kWideStages * kWideStageBytes + 256 + 1024;
+constexpr int kWideBN = 512;
+constexpr int kWideThreads = 320;
+
+template <typename OutT>
+__global__ void __launch_bounds__(kWideThreads, 1)
+gemm_tn_pair_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, OutT* __restrict__ c,
+                         const GemmParams p, const uint32_t idesc, const int vec_ok, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kWideStages * kWideStageBytes);
+  uint64_t* empty_bar = full_bar + kWideStages;
+  uint64_t* tmem_full_bar = empty_bar + kWideStages;   // [2]: one per accumulator half
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tma_a);
+    prefetch_tensormap(&tma_b);
+    for (int s = 0; s < kWideStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(&tmem_full_bar[h], 1);
+      mbar_init(&tmem_empty_bar[h], 8);  // 4 epilogue warps of this half in each of the two CTAs
+    }
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(tmem_slot, kTmemCols);
+    tmem_relinquish<2>();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  const int m_blocks = (p.m_valid + kPairBM - 1) / kPairBM;
+  const int n_blocks = (p.n_valid + kWideBN - 1) / kWideBN;
+  const int num_tiles = m_blocks * n_blocks;
+  const int num_kb = p.k_blocks_per_seg * p.num_segs;
+  const int group = max(p.group_m / 2, 1);
+
+  auto coords = [&](int t, int& m_blk, int& n_blk) {
+    const int group_size = group * n_blocks;
+    const int g = t / group_size;
+    const int first_m = g * group;
+    const int gm = min(m_blocks - first_m, group);
+    const int r = t - g * group_size;
+    m_blk = first_m + r % gm;
+    n_blk = r / gm;
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        int m_blk, n_blk;
+        coords(t, m_blk, n_blk);
+        const int a_row = m_blk * kPairBM + static_cast<int>(rank) * 128;
+        const int b_row = n_blk * kWideBN + static_cast<int>(rank) * 128;
+        int seg = 0, kb_in_seg = 0;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait<true>(&empty_bar[stage], phase ^ 1u, status, SILE_ERR_TIMEOUT, 1 + 4 * rank)) { ok = false; break; }
+          uint8_t* sa = smem + stage * kWideStageBytes;
+          uint8_t* sb = sa + kPairABytes;
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * kWideStageBytes);
+          const int x = kb_in_seg * kBK;
+          tma_load_2d_pair(sa, &tma_a, &full_bar[stage], 0, x, p.a_seg_row[seg] + a_row);
+          tma_load_2d_pair(sb, &tma_b, &full_bar[stage], 0, x, p.b_seg_row[seg] + b_row);
+          tma_load_2d_pair(sb + kPairBBytes, &tma_b, &full_bar[stage], 0, x, p.b_seg_row[seg] + b_row + 256);
+          if (++kb_in_seg == p.k_blocks_per_seg) { kb_in_seg = 0; ++seg; }
+          if (++stage == kWideStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+        const uint32_t tile_phase = it & 1;
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          if (!mbar_wait<true>(&full_bar[stage], phase, status, SILE_ERR_TIMEOUT, 3)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * kWideStageBytes);
+          const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (kb == 0) {
+              // the previous tile's half h must have been drained by both CTAs' epilogue warps
+              if (!mbar_wait<true>(&tmem_empty_bar[h], tile_phase ^ 1u, status, SILE_ERR_TIMEOUT, 2)) { ok = false; break; }
+              tcgen05_fence_after();
+            }
+            const uint64_t bdesc = make_smem_desc_sw128(sa + kPairABytes + h * kPairBBytes, 16, 1024);
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k)
+              umma_ss_f16<2>(tmem_base + h * 256, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (kb == num_kb - 1) {
+              umma_commit_pair_to(&tmem_full_bar[h], 0);
+              umma_commit_pair_to(&tmem_full_bar[h], 1);
+            }
+          }
+          if (!ok) break;
+          umma_commit_pair_to(&empty_bar[stage], 0);
+          umma_commit_pair_to(&empty_bar[stage], 1);
+          if (++stage == kWideStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (both CTAs; warps 2..5 drain half 0, warps 6..9 half 1) ----------------
+    const int quarter = warp & 3;
+    const int h = (warp - 2) >> 2;
+    int it = 0;
+    bool ok = true;
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+      int m_blk, n_blk;
+      coords(t, m_blk, n_blk);
+      if (!mbar_wait<true>(&tmem_full_bar[h], it & 1, status, SILE_ERR_TIMEOUT, 4 + 4 * rank)) { ok = false; }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row0 = m_blk * kPairBM + static_cast<int>(rank) * 128;
+      const int row = row0 + quarter * 32 + lane;
+      const int col_base = n_blk * kWideBN + h * 256;
+      const bool tile_fast = vec_ok && !p.masked && (row0 + 128 <= p.m_valid) && (col_base + 256 <= p.n_valid);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + h * 256;
+#pragma unroll 1
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + ch * 32, r);
+        tcgen05_wait_ld();
+        if (tile_fast || col_base + ch * 32 < p.n_valid) store_chunk<OutT>(c, p, row, col_base + ch * 32, r, tile_fast);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(&tmem_empty_bar[h], 0);
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    if (*reinterpret_cast<volatile int*>(status) != 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) {
+      }
+    }
+    tmem_dealloc<2>(tmem_base, kTmemCols);
+  }
+}
+
 // ---- f32 -> (hi, lo) bf16 split pre-pass -----------------------------------------
 // A: [M,K] f32 row-major -> hi/lo [M,Kp] bf16, zero for k >= k_eff.
 __global__ void split_rows_kernel(const float* __restrict__ src, int64_t ld, __nv_bfloat16* __restrict__ hi,
@@ -386,6 +748,109 @@ int launch_typed(const CUtensorMap& ta, const CUtensorMap& tb, void* c, const Ge
   return SILE_OK;
 }
 
+template <typename OutT, bool kWide>
+struct PairKernel {
+  static auto fn() {
+    if constexpr (kWide) return &gemm_tn_pair_wide_kernel<OutT>;
+    else return &gemm_tn_pair_kernel<OutT>;
+  }
+  static constexpr int threads = kWide ? kWideThreads : kNumThreads;
+  static constexpr int smem = kWide ? kWideSmemBytes : kPairSmemBytes;
+  static constexpr int bn = kWide ? kWideBN : kBN;
+};
+
+template <typename OutT, bool kWide>
+void pair_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int clusters, cudaStream_t stream) {
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg->gridDim = dim3(2 * clusters);
+  cfg->blockDim = dim3(PairKernel<OutT, kWide>::threads);
+  cfg->dynamicSmemBytes = PairKernel<OutT, kWide>::smem;
+  cfg->stream = stream;
+  cfg->attrs = attr;
+  cfg->numAttrs = 1;
+}
+
+// Number of 2-CTA clusters of a pair kernel that can be resident at once (0 = clusters cannot
+// be scheduled on this device).  Queried once per kernel instantiation.
+template <typename OutT, bool kWide>
+int pair_max_clusters() {
+  static int max_clusters = -1;
+  if (max_clusters >= 0) return max_clusters;
+  auto fn = PairKernel<OutT, kWide>::fn();
+  if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, PairKernel<OutT, kWide>::smem) != cudaSuccess) {
+    cudaGetLastError();
+    return max_clusters = 0;
+  }
+  int sms = 148, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  pair_config<OutT, kWide>(&cfg, attr, sms / 2, nullptr);
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  return max_clusters = n;
+}
+
+template <bool kWide>
+int pair_max_clusters_for(int out_dtype) {
+  switch (out_dtype) {
+    case SILE_DTYPE_F32: return pair_max_clusters<float, kWide>();
+    case SILE_DTYPE_BF16: return pair_max_clusters<__nv_bfloat16, kWide>();
+    default: return pair_max_clusters<__half, kWide>();
+  }
+}
+
+template <typename OutT, bool kWide>
+int launch_pair_typed(const CUtensorMap& ta, const CUtensorMap& tb, void* c, const GemmParams& gp, uint32_t idesc, int vec_ok,
+                      int* status, cudaStream_t stream) {
+  const int m_blocks = (gp.m_valid + kPairBM - 1) / kPairBM;
+  const int n_blocks = (gp.n_valid + PairKernel<OutT, kWide>::bn - 1) / PairKernel<OutT, kWide>::bn;
+  const int tiles = m_blocks * n_blocks;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  pair_config<OutT, kWide>(&cfg, attr, std::min(tiles, pair_max_clusters<OutT, kWide>()), stream);
+  SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, PairKernel<OutT, kWide>::fn(), ta, tb, static_cast<OutT*>(c), gp, idesc, vec_ok, status));
+  return SILE_OK;
+}
+
+template <bool kWide>
+int launch_pair(int out_dtype, const CUtensorMap& ta, const CUtensorMap& tb, void* c, const GemmParams& gp, uint32_t idesc, int vec_ok,
+                int* status, cudaStream_t stream) {
+  switch (out_dtype) {
+    case SILE_DTYPE_F32: return launch_pair_typed<float, kWide>(ta, tb, c, gp, idesc, vec_ok, status, stream);
+    case SILE_DTYPE_BF16: return launch_pair_typed<__nv_bfloat16, kWide>(ta, tb, c, gp, idesc, vec_ok, status, stream);
+    default: return launch_pair_typed<__half, kWide>(ta, tb, c, gp, idesc, vec_ok, status, stream);
+  }
+}
+
+// SILE_CUDA_GEMM_KERNEL = single | pair | wide overrides the kernel choice (tuning, tests).
+// Read on every launch so a process can switch.
+int forced_kernel() {
+  const char* e = getenv("SILE_CUDA_GEMM_KERNEL");
+  if (!e) return 0;
+  if (!strcmp(e, "single")) return 1;
+  if (!strcmp(e, "pair")) return 2;
+  if (!strcmp(e, "wide")) return 3;
+  return 0;
+}
+
+// 128-row blocks per raster group (SILE_CUDA_GEMM_GROUP_M overrides, for tuning).
+int raster_group_m() {
+  static const int g = [] {
+    const char* e = getenv("SILE_CUDA_GEMM_GROUP_M");
+    const int v = e ? atoi(e) : 0;
+    return v > 0 ? v : kGroupM;
+  }();
+  return g;
+}
+
 }  // namespace
 
 size_t gemm_workspace_bytes(const GemmProblem& p) {
@@ -433,12 +898,29 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
   const long long total_logical = static_cast<long long>(p.m / bm) * (p.n / bn);
   gp.ntg = p.num_threadgroups;
   gp.masked = p.num_threadgroups < total_logical ? 1 : 0;
+  gp.group_m = raster_group_m();
 
   CUtensorMap ta, tb;
   const bool bf16 = p.in_dtype != SILE_DTYPE_F16;
   const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  // Kernel choice, from measurements on 1024^3 .. 8192^3 problems: the wide pair kernel
+  // (256 x 512 tiles) wins whenever it has enough tiles to occupy most of the 74 SM pairs; with
+  // at most 256 output columns the 256 x 256 pair kernel takes its place; small problems keep
+  // the single-CTA kernel, whose 128 x 256 tiles spread over more SMs.  In a pair each CTA
+  // stages 128-row boxes of B, so the B box differs from the single-CTA kernel's.
+  const int forced = forced_kernel();
+  const int64_t tiles_pair = ((e.m_valid + kPairBM - 1) / kPairBM) * ((e.n_valid + kBN - 1) / kBN);
+  const int64_t tiles_wide = ((e.m_valid + kPairBM - 1) / kPairBM) * ((e.n_valid + kWideBN - 1) / kWideBN);
+  constexpr int64_t kMinPairTiles = 48;
+  bool use_wide = false, use_pair = false;
+  if (forced == 3 || (forced == 0 && e.n_valid > kBN && tiles_wide >= kMinPairTiles)) {
+    use_wide = e.m_valid > kBM && pair_max_clusters_for<true>(p.out_dtype) > 0;
+  } else if (forced == 2 || (forced == 0 && e.n_valid <= kBN && tiles_pair >= kMinPairTiles)) {
+    use_pair = e.m_valid > kBM && pair_max_clusters_for<false>(p.out_dtype) > 0;
+  }
+  use_pair = use_pair || use_wide;
   const uint32_t box_a[2] = {kBK, kBM};
-  const uint32_t box_b[2] = {kBK, kBN};
+  const uint32_t box_b[2] = {kBK, use_pair ? 128u : static_cast<uint32_t>(kBN)};
 
   if (p.in_dtype == SILE_DTYPE_F32) {
     if (e.k_eff == 0) {
@@ -506,6 +988,13 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
     gp.k_blocks_per_seg = static_cast<int>((e.k_eff + kBK - 1) / kBK);
   }
 
+  const size_t out_elt = p.out_dtype == SILE_DTYPE_F32 ? 4 : 2;
+  const int vec_ok = (reinterpret_cast<uintptr_t>(p.c) % 16 == 0) && ((gp.ldc * out_elt) % 16 == 0);
+  if (use_pair) {
+    const uint32_t idesc2 = make_idesc_f16(kPairBM, kBN, bf16, false, false);
+    return use_wide ? launch_pair<true>(p.out_dtype, ta, tb, p.c, gp, idesc2, vec_ok, status, stream)
+                    : launch_pair<false>(p.out_dtype, ta, tb, p.c, gp, idesc2, vec_ok, status, stream);
+  }
   const uint32_t idesc = make_idesc_f16(kBM, kBN, bf16, false, false);
   const int num_tiles = gp.m_blocks * gp.n_blocks;
   int dev = 0, sms = 148;
@@ -513,8 +1002,6 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
   SILE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int grid = std::min(num_tiles, sms);
 
-  const size_t out_elt = p.out_dtype == SILE_DTYPE_F32 ? 4 : 2;
-  const int vec_ok = (reinterpret_cast<uintptr_t>(p.c) % 16 == 0) && ((gp.ldc * out_elt) % 16 == 0);
   switch (p.out_dtype) {
     case SILE_DTYPE_F32: return launch_typed<float>(ta, tb, p.c, gp, idesc, vec_ok, status, grid, stream);
     case SILE_DTYPE_BF16: return launch_typed<__nv_bfloat16>(ta, tb, p.c, gp, idesc, vec_ok, status, grid, stream);
@@ -643,6 +1130,7 @@ extern "C" int sile_cuda_matmul_f32_noalloc(const float* a, const float* b, floa
   gp.ltiles_n = static_cast<int>(n / p.bn);
   gp.ntg = INT64_MAX;
   gp.masked = 0;
+  gp.group_m = kGroupM;
   gp.num_segs = 3;
   gp.k_blocks_per_seg = static_cast<int>(e.kp / kBK);
   gp.a_seg_row[0] = static_cast<int>(m); gp.b_seg_row[0] = 0;
@@ -663,7 +1151,7 @@ extern "C" int sile_cuda_matmul_f32_noalloc(const float* a, const float* b, floa
     SILE_CUDA_TRY(cudaMemcpy(&st, nd.status, sizeof(int), cudaMemcpyDeviceToHost));
     if (st != 0) {
       SILE_CUDA_TRY(cudaMemset(nd.status, 0, sizeof(int)));
-      return fail(st, "matmul_f32_noalloc: a device-side wait ran out (code %d); the result is invalid", st);
+      return fail(st & 0xff, "matmul_f32_noalloc: a device-side wait ran out (code %d); the result is invalid", st & 0xff);
     }
   }
   return SILE_OK;

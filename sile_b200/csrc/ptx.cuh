@@ -36,6 +36,17 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---- cluster ----------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // ---- mbarrier ---------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -89,10 +100,11 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
   return ok != 0;
 }
 
-// Bounded wait.  Returns false after kWaitLimitNs (recording `code` in *status,
-// first writer wins) or as soon as another thread has recorded a failure.
+// Bounded wait.  Returns false after kWaitLimitNs, or as soon as another thread has recorded a
+// failure.  On either exit it ORs `code` (low byte) and bit (8 + site) into *status, so the word
+// names every wait site that was stuck when the kernel gave up.
 template <bool kCluster = false>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code, int site = 0) {
 #pragma unroll 1
   for (int i = 0; i < 128; ++i) {
     if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
@@ -104,9 +116,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     for (int i = 0; i < 512; ++i) {
       if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     }
-    if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
-      atomicCAS(status, 0, code);
+    if (*reinterpret_cast<volatile int*>(status) != 0 || globaltimer_ns() - t0 > kWaitLimitNs) {
+      atomicOr(status, code | (1 << (8 + (site & 15))));
       return false;
     }
   }
@@ -128,14 +139,20 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// Shared-memory addresses inside a CTA pair (cluster ranks 2i, 2i+1): bit 24 of a shared::cta
+// address names the CTA within the pair, so the same offset in the even / odd CTA is reached by
+// clearing / setting that bit.
+constexpr uint32_t kPairPeerBit = 0x01000000u;
+__device__ __forceinline__ uint32_t pair_addr(const void* p, uint32_t cta_in_pair) {
+  const uint32_t a = smem_u32(p) & ~kPairPeerBit;
+  return cta_in_pair ? (a | kPairPeerBit) : a;
+}
 // In a CTA pair: the completion is signalled on the barrier at the same offset
-// in the shared memory of cluster CTA `bar_cta` (the MMA-issuing CTA).
+// in the shared memory of pair CTA `bar_cta` (the MMA-issuing CTA).
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint64_t* bar, uint32_t bar_cta, int32_t x, int32_t y) {
-  uint32_t remote_bar;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(smem_u32(bar)), "r"(bar_cta));
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(remote_bar), "r"(x), "r"(y)
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(pair_addr(bar, bar_cta)), "r"(x), "r"(y)
       : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int32_t x, int32_t y) {
@@ -226,11 +243,9 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // CTA-pair form: arrives on the barrier at the same offset in the shared memory of
-// cluster CTA `cta_rank` (issue once per CTA that must be told).
-__device__ __forceinline__ void umma_commit_pair_to(uint64_t* bar, uint32_t cta_rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(cta_rank));
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(remote) : "memory");
+// pair CTA `cta_in_pair` (issue once per CTA that must be told).
+__device__ __forceinline__ void umma_commit_pair_to(uint64_t* bar, uint32_t cta_in_pair) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(pair_addr(bar, cta_in_pair)) : "memory");
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane (base+i).

@@ -133,6 +133,24 @@ def test_bf16_shapes(sb, oracle, m, n, k, col_major):
     assert rel_err(got, want) < BF16_TOL
 
 
+@pytest.mark.parametrize("kernel", ["single", "pair", "wide"])
+def test_every_kernel_variant(sb, oracle, kernel, monkeypatch):
+    """The single-CTA, CTA-pair (256x256) and wide CTA-pair (256x512) kernels on the same
+    problems: ragged f32 with a K remainder and a short grid, and bf16 with several tiles."""
+    monkeypatch.setenv("SILE_CUDA_GEMM_KERNEL", kernel)
+    m, n, k, bm, bn, bk = 700, 1100, 328, 4, 4, 8
+    a, b = uniform((m, k), 31), uniform((k, n), 32)
+    sentinel = np.full((m, n), -7.0, np.float32)
+    ntg = (m // bm) * (n // bn) - 37
+    got = _gpu_matmul_f32(sb, a, b, bm, bn, bk, grid=(ntg, 1, 1), c_init=sentinel)
+    want = oracle.matmul(a, b, bm, bn, bk)
+    mask = tile_mask(m, n, bm, bn, range(ntg))
+    assert (got[~mask] == -7.0).all()
+    assert rel_err(got[mask], want[mask]) < F32_TOL
+    got, a_up, b_up = _bf16_case(sb, oracle, 1024, 1536, 512, True, seed=5)
+    assert rel_err(got, oracle.matmul(a_up, b_up, 1, 1, 1)) < BF16_TOL
+
+
 def test_bf16_f32_out_is_tight(sb, oracle):
     # with f32 output only accumulation order differs from the oracle
     got, a_up, b_up = _bf16_case(sb, oracle, 256, 512, 512, True, out_bf16=False)
