@@ -420,7 +420,7 @@ def main():
         "bound": "tensor", "achieved": achieved, "peak": peaks[peak_key], "unit": "TFLOP/s",
         "frac": achieved / peaks[peak_key], "traffic": GEMM_DRAM_TRAFFIC_BYTES if p == 1 else None,
         "peak_source": f"{peak_src} {peak_key}", "frac_of_nominal_dense_bf16": achieved / NOMINAL_BF16_TFLOPS,
-        "kernel": "gemm_tn_kernel<bf16>", "algorithmic_flops_per_launch": per_gpu_flops,
+        "kernel": "gemm_tn_pair_wide_kernel<bf16>", "algorithmic_flops_per_launch": per_gpu_flops,
     }
     if p > 1:
         roofline["note"] = "per-GPU share of the whole step (GEMM chunks + all-gather + unshard), not the kernel alone"
