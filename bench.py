@@ -275,7 +275,9 @@ def main():
     sb._lib.lib()  # fail loudly if the extension is missing
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
+                                timeout=datetime.timedelta(seconds=180))
     if args.workload != "gemm_bf16_8192":
         if rank == 0:
             peaks, _ = load_peaks()
@@ -356,10 +358,11 @@ def main():
     e1.record()
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
-    # keep the GPU busy a little longer so the sampler sees the loaded clock even for short runs
-    if sampler is not None and len(sampler.samples) < 8:
-        t_end = time.time() + 0.25
-        while time.time() < t_end:
+    # A short timed region gives the 10 ms clock sampler too few readings under load: keep the
+    # same work running for ~0.25 s more.  The count derives from the max-reduced time, so every
+    # rank runs the same number of (collective) steps.
+    if ms_total < 250.0:
+        for _ in range(int(min(5000, 250.0 / max(ms_total / args.steps, 1e-3)))):
             step()
         torch.cuda.synchronize()
     clocks = sampler.stop() if sampler is not None else None
