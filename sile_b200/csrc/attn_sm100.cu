@@ -164,24 +164,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       const uint32_t v_addr = smem_u32(smem + kSmemV);
       bool ok = true;
 
+      // Descriptors are built once; inside the unrolled loops only a constant is added to the
+      // 14-bit start-address field, so issuing one MMA costs a handful of instructions (a
+      // 128 x 128 x 16 MMA runs for 64 cycles: anything slower than that starves the tensor pipe).
+      const uint64_t q_desc[2] = {make_smem_desc_sw128(q_addr, 16, 1024), make_smem_desc_sw128(q_addr + kTileBytes, 16, 1024)};
+      const uint64_t k_desc[2] = {make_smem_desc_sw128(k_addr, 16, 1024), make_smem_desc_sw128(k_addr + kTileBytes, 16, 1024)};
+      const uint64_t v_desc[2] = {make_smem_desc_sw128(v_addr, kPanelBytes, 1024),
+                                  make_smem_desc_sw128(v_addr + kTileBytes, kPanelBytes, 1024)};
+
       auto issue_s = [&](int t, int st) {
         // S_t = Q_t (128 x 128, two 64-wide k panels) * K_st^T
+        const uint64_t da = q_desc[t], db = k_desc[st];
+        const uint32_t d = tmem_s[t];
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-          const uint64_t da = make_smem_desc_sw128(q_addr + t * kTileBytes + off, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(k_addr + st * kTileBytes + off, 16, 1024);
-          umma_ss_f16<1>(tmem_s[t], da, db, idesc_s, kk != 0 ? 1u : 0u);
+          constexpr int kPanelUnits = kPanelBytes >> 4;
+          const uint32_t off = (kk >> 2) * kPanelUnits + (kk & 3) * 2;  // in 16-byte units
+          umma_ss_f16<1>(d, da + off, db + off, idesc_s, kk != 0 ? 1u : 0u);
         }
         umma_commit<1>(&s_full[t]);
       };
       auto issue_pv = [&](int t, int st, bool accumulate) {
         // O_t += P_t (TMEM, 8 columns per 16 keys) * V_st (rows = keys, 2048 B per 16 keys; d panels 16 KiB apart)
+        const uint64_t db = v_desc[st];
+        const uint32_t d = tmem_o[t], a = tmem_s[t];
+        umma_ts_f16(d, a, db, idesc_o, accumulate ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < kBlockKV / 16; ++kk) {
-          const uint64_t db = make_smem_desc_sw128(v_addr + st * kTileBytes + kk * 2048, kPanelBytes, 1024);
-          umma_ts_f16(tmem_o[t], tmem_s[t] + kk * 8, db, idesc_o, (accumulate || kk != 0) ? 1u : 0u);
-        }
+        for (int kk = 1; kk < kBlockKV / 16; ++kk) umma_ts_f16(d, a + kk * 8, db + kk * 128, idesc_o, 1u);
         umma_commit<1>(&o_done[t]);
       };
 
