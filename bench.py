@@ -248,7 +248,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--chunks", type=int, default=4, help="M chunks used to overlap the all-gather (N > 1)")
+    ap.add_argument("--chunks", type=int, default=4, help="M chunks used to overlap the NCCL all-gather (N > 1)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "nccl"],
+                    help="N > 1: how C is assembled on every rank (fused = stores from the GEMM epilogue)")
     ap.add_argument("--no-extras", action="store_true", help="skip the attention / f32 side measurements")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="gemm_bf16_8192", choices=["gemm_bf16_8192"] + sorted(SIDE_WORKLOADS),
@@ -268,6 +270,7 @@ def main():
     import torch
     import torch.distributed as dist
     import sile_b200 as sb
+    import sile_b200.sharding  # noqa: F401
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
@@ -300,38 +303,67 @@ def main():
     b_shard = b_full[rank * nshard:(rank + 1) * nshard].contiguous()
     if p > 1:
         del b_full
-    c = torch.zeros(n, n, device=dev, dtype=torch.bfloat16)
+    c = torch.zeros(n, n, device=dev, dtype=torch.bfloat16) if p == 1 else None
     bm, bn, bk = ORACLE_TILE
     launches_per_step = 1
 
+    exchange = "none"
     if p == 1:
         kl = sb.matmul(a, b_shard, c, bm, bn, bk, b_layout=sb._lib.LAYOUT_COL_MAJOR)
 
         def step():
             kl.apply()
     else:
-        nch = max(1, args.chunks)
-        rows = n // nch
-        cs = torch.zeros(n, nshard, device=dev, dtype=torch.bfloat16)
-        gathered = [torch.empty(p, rows, nshard, device=dev, dtype=torch.bfloat16) for _ in range(nch)]
-        comm = torch.cuda.Stream(device=dev)
-        events = [torch.cuda.Event() for _ in range(nch)]
-        done = torch.cuda.Event()
-        launches_per_step = 2 * nch
+        fused = None
+        if args.exchange in ("auto", "fused"):
+            try:
+                # C lives in symmetric memory: every rank maps every rank's buffer, and the GEMM
+                # epilogue stores its column block straight into all of them over NVLink.
+                import torch.distributed._symmetric_memory as symm_mem
+                c = symm_mem.empty((n, n), dtype=torch.bfloat16, device=dev)
+                hdl = symm_mem.rendezvous(c, dist.group.WORLD)
+                ptrs = [int(x) for x in hdl.buffer_ptrs]
+                c.zero_()
+                fused = (hdl, ptrs)
+            except Exception as e:  # no peer mapping on this box: all-gather through NCCL instead
+                if args.exchange == "fused":
+                    raise
+                if rank == 0:
+                    print(f"symmetric memory unavailable ({e!r}); using the NCCL all-gather path", file=sys.stderr)
+                c = torch.zeros(n, n, device=dev, dtype=torch.bfloat16)
+        if fused is not None:
+            exchange = "fused epilogue: st.global into every rank's C over NVLink (symmetric memory), one device barrier per step"
+            hdl, ptrs = fused
+            launches_per_step = 1
 
-        def step():
-            main_stream = torch.cuda.current_stream()
-            comm.wait_stream(main_stream)
-            for i in range(nch):
-                r0 = i * rows
-                sb.matmul_shard(a[r0:r0 + rows], b_shard, cs[r0:r0 + rows], 0, nshard, bm, bn, bk)
-                events[i].record(main_stream)
-                with torch.cuda.stream(comm):
-                    comm.wait_event(events[i])
-                    dist.all_gather_into_tensor(gathered[i], cs[r0:r0 + rows])
-                    sb.unshard_columns(c[r0:r0 + rows], gathered[i], stream=comm)
-            done.record(comm)
-            main_stream.wait_event(done)
+            def step():
+                sb.matmul_allgather(a, b_shard, ptrs, rank, n, torch.bfloat16, bm, bn, bk)
+                hdl.barrier(channel=0, timeout_ms=20000)
+        else:
+            exchange = f"{args.chunks} M-chunks, NCCL all-gather of C overlapped with compute, unshard kernel"
+            if c is None:
+                c = torch.zeros(n, n, device=dev, dtype=torch.bfloat16)
+            chunks = sb.sharding.row_chunks(n, max(1, args.chunks))
+            nch = len(chunks)
+            cs = torch.zeros(n, nshard, device=dev, dtype=torch.bfloat16)
+            gathered = [torch.empty(p, rc, nshard, device=dev, dtype=torch.bfloat16) for _, rc in chunks]
+            comm = torch.cuda.Stream(device=dev)
+            events = [torch.cuda.Event() for _ in range(nch)]
+            done = torch.cuda.Event()
+            launches_per_step = 2 * nch
+
+            def step():
+                main_stream = torch.cuda.current_stream()
+                comm.wait_stream(main_stream)
+                for i, (r0, rc) in enumerate(chunks):
+                    sb.matmul_shard(a[r0:r0 + rc], b_shard, cs[r0:r0 + rc], 0, nshard, bm, bn, bk)
+                    events[i].record(main_stream)
+                    with torch.cuda.stream(comm):
+                        comm.wait_event(events[i])
+                        dist.all_gather_into_tensor(gathered[i], cs[r0:r0 + rc])
+                        sb.unshard_columns(c[r0:r0 + rc], gathered[i], stream=comm)
+                done.record(comm)
+                main_stream.wait_event(done)
 
     def barrier():
         if p > 1:
@@ -434,7 +466,7 @@ def main():
         "dtype": "bf16", "data": "synthetic",
         "config": {
             "workload": "gemm_bf16_8192: M=N=K=8192, A row-major, B column-major, N(0,1)/sqrt(K) bf16, f32 accumulate, bf16 out",
-            "parallelism": f"N-sharded x{p}" + ("" if p == 1 else f", {args.chunks} M-chunks, NCCL all-gather of C overlapped with compute"),
+            "parallelism": f"N-sharded x{p}" + ("" if p == 1 else f"; {exchange}"),
             "l2": "inputs (2 x 128 MiB) and output (128 MiB) exceed the 126 MB L2; no flush between steps",
             "per_gpu_tflops": value / p,
         },

@@ -131,6 +131,20 @@ int sile_cuda_matmul_shard(const SileKernelDesc* desc, const void* a, const void
                            int64_t m, int64_t n_total, int64_t k, int64_t n_begin, int64_t n_count,
                            void* stream);
 
+/* The same column-block matmul with the all-gather folded into its epilogue: rank
+ * `rank` of `world` (<= 8) computes its block and stores every element into the
+ * full [M, n_total] row-major buffer of EVERY rank.  c_peers[i] is the base of
+ * rank i's buffer as mapped into this process (for instance the buffer_ptrs of
+ * a torch symmetric-memory allocation; c_peers[rank] is the local one).  Stores
+ * to peers travel over NVLink as plain st.global from the epilogue warps; the
+ * kernel waits on no other GPU.  When the call has completed on every rank and
+ * the ranks have synchronised (the caller's barrier), each holds the whole C.
+ * 16-bit operands, column-major B, N divisible by world, M > 128 and more than
+ * 256 columns per rank. */
+int sile_cuda_matmul_allgather(const SileKernelDesc* desc, const void* a, const void* b_shard,
+                               void* const* c_peers, int32_t world, int32_t rank, int64_t m,
+                               int64_t n_total, int64_t k, void* stream);
+
 /* Lays the rank-major result of an all-gather of packed column blocks,
  * src[parts][rows][cols], out as one row-major matrix dst[rows][parts*cols].
  * `dtype` is a SILE_DTYPE_* giving the element size. */

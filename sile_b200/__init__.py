@@ -4,7 +4,7 @@ The product is ``lib/libsile_cuda.so`` (C ABI in ``include/sile_cuda.h``); this 
 is the thin Python front end the tests and the bench use to reach it."""
 from . import _lib, api  # noqa: F401
 from .api import (KernelLauncher, SileError, attention, bind_consts, kernel_call, make_desc,  # noqa: F401
-                  matmul, matmul_shard, matvec, parallel_reduce, relu, softmax, synchronize,
+                  matmul, matmul_allgather, matmul_shard, matvec, parallel_reduce, relu, softmax, synchronize,
                   unshard_columns, vec_add)
 from .build import build  # noqa: F401
 

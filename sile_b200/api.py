@@ -183,3 +183,17 @@ def unshard_columns(dst, src, stream=None) -> None:
     parts, rows, cols = src.shape
     _check(_lib.lib().sile_cuda_unshard_columns(dst.data_ptr(), src.data_ptr(), parts, rows, cols,
                                                 _dtype_code(src), _stream_handle(stream)))
+
+
+def matmul_allgather(a, b_shard, c_ptrs, rank: int, n_total: int, out_dtype, bm=1, bn=1, bk=1, stream=None) -> None:
+    """Column-block matmul whose epilogue stores the block into every rank's full C.
+
+    ``c_ptrs`` lists the device addresses of each rank's [M, n_total] buffer as mapped into
+    this process (``c_ptrs[rank]`` is the local one); ``out_dtype`` is a torch dtype."""
+    import torch
+    code = {torch.float32: DTYPE_F32, torch.bfloat16: DTYPE_BF16, torch.float16: DTYPE_F16}[out_dtype]
+    desc = make_desc(OP_MATMUL, _dtype_code(a), code, LAYOUT_COL_MAJOR, consts=(bm, bn, bk))
+    m, k = a.shape
+    arr = (C.c_void_p * len(c_ptrs))(*[int(p) for p in c_ptrs])
+    _check(_lib.lib().sile_cuda_matmul_allgather(C.byref(desc), a.data_ptr(), b_shard.data_ptr(), arr, len(c_ptrs), rank,
+                                                 m, n_total, k, _stream_handle(stream)))

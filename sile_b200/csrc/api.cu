@@ -474,6 +474,35 @@ int sile_cuda_matmul_shard(const SileKernelDesc* desc, const void* a, const void
   return rc;
 }
 
+int sile_cuda_matmul_allgather(const SileKernelDesc* desc, const void* a, const void* b_shard, void* const* c_peers, int32_t world,
+                               int32_t rank, int64_t m, int64_t n_total, int64_t k, void* stream) {
+  if (int rc = validate_desc(desc)) return rc;
+  if (int rc = check_device()) return rc;
+  if (desc->op != SILE_OP_MATMUL) return fail(SILE_ERR_INVALID, "matmul_allgather: description is not a matmul");
+  if (!a || !b_shard || !c_peers) return fail(SILE_ERR_INVALID, "null buffer");
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(SILE_ERR_INVALID, "matmul_allgather: bad rank %d of %d (at most 8)", rank, world);
+  if (n_total % world != 0) return fail(SILE_ERR_INVALID, "matmul_allgather: N = %lld does not split into %d column blocks", (long long)n_total, world);
+  if (desc->in_dtype == SILE_DTYPE_F32 || desc->b_layout != SILE_LAYOUT_COL_MAJOR)
+    return fail(SILE_ERR_UNSUPPORTED, "matmul_allgather: 16-bit operands with column-major B only");
+  const int64_t n_count = n_total / world, n_begin = n_count * rank;
+  GemmProblem p;
+  p.a = a; p.b = b_shard;
+  p.m = m; p.n = n_count; p.k = k; p.ldc = n_total;
+  p.in_dtype = desc->in_dtype; p.out_dtype = desc->out_dtype; p.b_layout = desc->b_layout;
+  p.bm = const_or_one(desc, 0); p.bn = const_or_one(desc, 1); p.bk = const_or_one(desc, 2);
+  const size_t off = static_cast<size_t>(n_begin) * dtype_size(desc->out_dtype);
+  for (int i = 0; i < world; ++i) {
+    if (!c_peers[i]) return fail(SILE_ERR_INVALID, "matmul_allgather: null destination %d", i);
+    p.peer_c[i] = static_cast<char*>(c_peers[i]) + off;
+  }
+  p.c = p.peer_c[rank];
+  p.num_peers = world;
+  p.peer_first = rank;
+  const int rc = gemm_launch(p, static_cast<cudaStream_t>(stream));
+  if (rc == SILE_OK) t_last_status = SILE_OK;
+  return rc;
+}
+
 int sile_cuda_unshard_columns(void* dst, const void* src, int64_t parts, int64_t rows, int64_t cols, int32_t dtype, void* stream) {
   if (int rc = check_device()) return rc;
   const int rc = unshard_columns_launch(dst, src, parts, rows, cols, static_cast<int>(dtype_size(dtype)), static_cast<cudaStream_t>(stream));

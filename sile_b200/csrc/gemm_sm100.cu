@@ -65,6 +65,21 @@ struct GemmParams {
   int group_m;  // 128-row blocks per raster group
 };
 
+// Destinations of the wide kernel's epilogue.  Normally one (the caller's C); for the fused
+// GEMM + all-gather every rank's buffer is listed (this GPU's own and its peers', reached over
+// NVLink through peer-mapped pointers) and every output element is stored into each of them,
+// starting with `first` so that ranks do not all hit the same peer at once.
+struct PeerOut {
+  void* ptr[8];  // same layout and leading dimension as C, already offset to the column block
+  int count;     // >= 1
+  int first;
+};
+// One tensor map per destination for the epilogue's TMA stores: 2-D {columns, rows} over the
+// destination starting at its column block, box = 128 bytes x 32 rows, 128-byte swizzle.
+struct OutMaps {
+  CUtensorMap map[8];
+};
+
 __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& m_blk, int& n_blk) {
   const int group_m = p.group_m;
   const int group_size = group_m * p.n_blocks;
@@ -456,17 +471,20 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 // K reaches the thousands).  Eight epilogue warps: four per accumulator half.
 constexpr int kWideStages = 4;
 constexpr int kWideStageBytes = kPairABytes + 2 * kPairBBytes;
-constexpr int kWideSmemBytes = kWideStages * kWideStageBytes + 256 + 1024;
+constexpr int kWideStagingBytes = 8 * 4096;  // one 32-row x 128-byte store box per epilogue warp
+constexpr int kWideSmemBytes = kWideStages * kWideStageBytes + kWideStagingBytes + 256 + 1024;
 constexpr int kWideBN = 512;
 constexpr int kWideThreads = 320;
 
 template <typename OutT>
 __global__ void __launch_bounds__(kWideThreads, 1)
 gemm_tn_pair_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, OutT* __restrict__ c,
-                         const GemmParams p, const uint32_t idesc, const int vec_ok, int* __restrict__ status) {
+                         const GemmParams p, const uint32_t idesc, const int vec_ok, int* __restrict__ status,
+                         const PeerOut peers, const __grid_constant__ OutMaps out_maps) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kWideStages * kWideStageBytes);
+  uint8_t* staging = smem + kWideStages * kWideStageBytes;  // 1024-byte aligned: matches the store maps' swizzle
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + kWideStagingBytes);
   uint64_t* empty_bar = full_bar + kWideStages;
   uint64_t* tmem_full_bar = empty_bar + kWideStages;   // [2]: one per accumulator half
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;        // [2]
@@ -586,8 +604,16 @@ gemm_tn_pair_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     __syncwarp();
   } else {
     // ---------------- epilogue (both CTAs; warps 2..5 drain half 0, warps 6..9 half 1) ----------------
+    // Whole tiles go out through shared memory: each warp converts 32 rows x 128 bytes, writes
+    // them in the 128-byte swizzle and lane 0 issues one TMA store per destination, so global
+    // (and NVLink) writes are full 128-byte lines and the data movement needs no further
+    // instructions.  TMEM is released as soon as the tile is in registers / staging, before the
+    // stores drain.  Ragged or launch-masked tiles take the per-thread store path.
     const int quarter = warp & 3;
     const int h = (warp - 2) >> 2;
+    constexpr int kBoxCols = 128 / static_cast<int>(sizeof(OutT));  // 64 (16-bit) or 32 (f32)
+    uint8_t* stage = staging + (warp - 2) * 4096;
+    const uint32_t stage_addr = smem_u32(stage);
     int it = 0;
     bool ok = true;
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
@@ -602,17 +628,79 @@ gemm_tn_pair_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const int col_base = n_blk * kWideBN + h * 256;
       const bool tile_fast = vec_ok && !p.masked && (row0 + 128 <= p.m_valid) && (col_base + 256 <= p.n_valid);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + h * 256;
+      if (tile_fast) {
 #pragma unroll 1
-      for (int ch = 0; ch < 8; ++ch) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + ch * 32, r);
-        tcgen05_wait_ld();
-        if (tile_fast || col_base + ch * 32 < p.n_valid) store_chunk<OutT>(c, p, row, col_base + ch * 32, r, tile_fast);
+        for (int b = 0; b < 256 / kBoxCols; ++b) {
+          uint32_t r[32], r2[32];
+          tmem_ld_32x32b_x32(taddr + b * kBoxCols, r);
+          if constexpr (kBoxCols == 64) tmem_ld_32x32b_x32(taddr + b * kBoxCols + 32, r2);
+          tcgen05_wait_ld();
+          if (b == 256 / kBoxCols - 1) {
+            // last read of this accumulator half: hand TMEM back before the stores are issued
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(&tmem_empty_bar[h], 0);
+          }
+          if (lane == 0) tma_store_wait_read<0>();  // the previous box has left the staging buffer
+          __syncwarp();
+          // row `lane` of the box: eight 16-byte chunks, chunk j stored at position j ^ (lane & 7)
+          const uint32_t row_addr = stage_addr + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint32_t v0, v1, v2, v3;
+            if constexpr (sizeof(OutT) == 4) {
+              v0 = r[4 * j]; v1 = r[4 * j + 1]; v2 = r[4 * j + 2]; v3 = r[4 * j + 3];
+            } else {
+              const uint32_t* src = (j < 4) ? (r + 8 * j) : (r2 + 8 * (j - 4));
+              if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+                v0 = pack_bf16x2(__uint_as_float(src[0]), __uint_as_float(src[1]));
+                v1 = pack_bf16x2(__uint_as_float(src[2]), __uint_as_float(src[3]));
+                v2 = pack_bf16x2(__uint_as_float(src[4]), __uint_as_float(src[5]));
+                v3 = pack_bf16x2(__uint_as_float(src[6]), __uint_as_float(src[7]));
+              } else {
+                __half2 h0 = __floats2half2_rn(__uint_as_float(src[0]), __uint_as_float(src[1]));
+                __half2 h1 = __floats2half2_rn(__uint_as_float(src[2]), __uint_as_float(src[3]));
+                __half2 h2 = __floats2half2_rn(__uint_as_float(src[4]), __uint_as_float(src[5]));
+                __half2 h3 = __floats2half2_rn(__uint_as_float(src[6]), __uint_as_float(src[7]));
+                v0 = *reinterpret_cast<uint32_t*>(&h0); v1 = *reinterpret_cast<uint32_t*>(&h1);
+                v2 = *reinterpret_cast<uint32_t*>(&h2); v3 = *reinterpret_cast<uint32_t*>(&h3);
+              }
+            }
+            const uint32_t dst = row_addr + ((j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v0), "r"(v1), "r"(v2), "r"(v3) : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            int d = peers.first;
+            for (int i = 0; i < peers.count; ++i) {
+              tma_store_2d(&out_maps.map[d], stage, col_base + b * kBoxCols, row0 + quarter * 32);
+              if (++d == peers.count) d = 0;
+            }
+            tma_store_commit();
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + ch * 32, r);
+          tcgen05_wait_ld();
+          if (col_base + ch * 32 < p.n_valid) {
+            int d = peers.first;
+            for (int i = 0; i < peers.count; ++i) {
+              store_chunk<OutT>(static_cast<OutT*>(peers.ptr[d]), p, row, col_base + ch * 32, r, false);
+              if (++d == peers.count) d = 0;
+            }
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(&tmem_empty_bar[h], 0);
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(&tmem_empty_bar[h], 0);
     }
+    if (lane == 0) tma_store_wait_all<0>();  // every store of this warp has been written out
+    __syncwarp();
   }
 
   tcgen05_fence_before();
@@ -809,24 +897,29 @@ int pair_max_clusters_for(int out_dtype) {
 
 template <typename OutT, bool kWide>
 int launch_pair_typed(const CUtensorMap& ta, const CUtensorMap& tb, void* c, const GemmParams& gp, uint32_t idesc, int vec_ok,
-                      int* status, cudaStream_t stream) {
+                      int* status, cudaStream_t stream, const PeerOut& peers, const OutMaps* out_maps) {
   const int m_blocks = (gp.m_valid + kPairBM - 1) / kPairBM;
   const int n_blocks = (gp.n_valid + PairKernel<OutT, kWide>::bn - 1) / PairKernel<OutT, kWide>::bn;
   const int tiles = m_blocks * n_blocks;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   pair_config<OutT, kWide>(&cfg, attr, std::min(tiles, pair_max_clusters<OutT, kWide>()), stream);
-  SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, PairKernel<OutT, kWide>::fn(), ta, tb, static_cast<OutT*>(c), gp, idesc, vec_ok, status));
+  if constexpr (kWide) {
+    SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, PairKernel<OutT, kWide>::fn(), ta, tb, static_cast<OutT*>(c), gp, idesc, vec_ok, status, peers,
+                                     *out_maps));
+  } else {
+    SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, PairKernel<OutT, kWide>::fn(), ta, tb, static_cast<OutT*>(c), gp, idesc, vec_ok, status));
+  }
   return SILE_OK;
 }
 
 template <bool kWide>
 int launch_pair(int out_dtype, const CUtensorMap& ta, const CUtensorMap& tb, void* c, const GemmParams& gp, uint32_t idesc, int vec_ok,
-                int* status, cudaStream_t stream) {
+                int* status, cudaStream_t stream, const PeerOut& peers, const OutMaps* out_maps) {
   switch (out_dtype) {
-    case SILE_DTYPE_F32: return launch_pair_typed<float, kWide>(ta, tb, c, gp, idesc, vec_ok, status, stream);
-    case SILE_DTYPE_BF16: return launch_pair_typed<__nv_bfloat16, kWide>(ta, tb, c, gp, idesc, vec_ok, status, stream);
-    default: return launch_pair_typed<__half, kWide>(ta, tb, c, gp, idesc, vec_ok, status, stream);
+    case SILE_DTYPE_F32: return launch_pair_typed<float, kWide>(ta, tb, c, gp, idesc, vec_ok, status, stream, peers, out_maps);
+    case SILE_DTYPE_BF16: return launch_pair_typed<__nv_bfloat16, kWide>(ta, tb, c, gp, idesc, vec_ok, status, stream, peers, out_maps);
+    default: return launch_pair_typed<__half, kWide>(ta, tb, c, gp, idesc, vec_ok, status, stream, peers, out_maps);
   }
 }
 
@@ -913,7 +1006,7 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
   const int64_t tiles_wide = ((e.m_valid + kPairBM - 1) / kPairBM) * ((e.n_valid + kWideBN - 1) / kWideBN);
   constexpr int64_t kMinPairTiles = 48;
   bool use_wide = false, use_pair = false;
-  if (forced == 3 || (forced == 0 && e.n_valid > kBN && tiles_wide >= kMinPairTiles)) {
+  if (forced == 3 || p.num_peers > 0 || (forced == 0 && e.n_valid > kBN && tiles_wide >= kMinPairTiles)) {
     use_wide = e.m_valid > kBM && pair_max_clusters_for<true>(p.out_dtype) > 0;
   } else if (forced == 2 || (forced == 0 && e.n_valid <= kBN && tiles_pair >= kMinPairTiles)) {
     use_pair = e.m_valid > kBM && pair_max_clusters_for<false>(p.out_dtype) > 0;
@@ -990,10 +1083,35 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
 
   const size_t out_elt = p.out_dtype == SILE_DTYPE_F32 ? 4 : 2;
   const int vec_ok = (reinterpret_cast<uintptr_t>(p.c) % 16 == 0) && ((gp.ldc * out_elt) % 16 == 0);
+  PeerOut peers{};
+  if (p.num_peers > 0) {
+    if (!use_wide) return fail(SILE_ERR_UNSUPPORTED, "matmul: the fused all-gather epilogue needs the wide pair kernel (M > 128, N > 256 per rank)");
+    for (int i = 0; i < p.num_peers; ++i) peers.ptr[i] = p.peer_c[i];
+    peers.count = p.num_peers;
+    peers.first = p.peer_first;
+  } else {
+    peers.ptr[0] = p.c;
+    peers.count = 1;
+    peers.first = 0;
+  }
   if (use_pair) {
     const uint32_t idesc2 = make_idesc_f16(kPairBM, kBN, bf16, false, false);
-    return use_wide ? launch_pair<true>(p.out_dtype, ta, tb, p.c, gp, idesc2, vec_ok, status, stream)
-                    : launch_pair<false>(p.out_dtype, ta, tb, p.c, gp, idesc2, vec_ok, status, stream);
+    if (!use_wide) return launch_pair<false>(p.out_dtype, ta, tb, p.c, gp, idesc2, vec_ok, status, stream, peers, nullptr);
+    static OutMaps zero_maps{};
+    OutMaps maps = zero_maps;
+    if (vec_ok) {
+      // Store maps: columns from the block's first column to the end of the row (the kernel
+      // only stores whole tiles inside the valid region through them), all M rows.
+      const CUtensorMapDataType odt = p.out_dtype == SILE_DTYPE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                    : p.out_dtype == SILE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+      const uint64_t odims[2] = {static_cast<uint64_t>(p.n), static_cast<uint64_t>(p.m)};
+      const uint64_t ostride[1] = {static_cast<uint64_t>(gp.ldc) * out_elt};
+      const uint32_t obox[2] = {static_cast<uint32_t>(128 / out_elt), 32};
+      for (int i = 0; i < peers.count; ++i)
+        if (int rc = encode_tensor_map(&maps.map[i], odt, 2, peers.ptr[i], odims, ostride, obox, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+    }
+    return launch_pair<true>(p.out_dtype, ta, tb, p.c, gp, idesc2, vec_ok, status, stream, peers, &maps);
   }
   const uint32_t idesc = make_idesc_f16(kBM, kBN, bf16, false, false);
   const int num_tiles = gp.m_blocks * gp.n_blocks;

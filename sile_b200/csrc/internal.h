@@ -45,6 +45,11 @@ struct GemmProblem {
   // which part of C is written (whole tiles only, K remainder dropped), never the CTA tiling.
   int64_t bm = 1, bn = 1, bk = 1;
   int64_t num_threadgroups = INT64_MAX;
+  // Fused all-gather: when num_peers > 0 every output element is stored into each peer_c[i]
+  // (same layout and leading dimension as c) instead of c; peer_first rotates the order.
+  void* peer_c[8] = {nullptr};
+  int num_peers = 0;
+  int peer_first = 0;
   void* workspace = nullptr;  // device scratch for the f32 split; see gemm_workspace_bytes
   size_t workspace_bytes = 0;
 };

@@ -204,3 +204,32 @@ def test_g3_bf16_8192_sampled_tiles_and_linearity(sb, oracle):
     sb.matmul((da * 2).contiguous(), db, dc2, 64, 64, 32, b_layout=sb._lib.LAYOUT_COL_MAJOR).apply()
     sb.synchronize()
     assert torch.equal(dc2, dc * 2)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_allgather_epilogue_on_one_gpu(sb, oracle, world):
+    """The GEMM whose epilogue stores its column block into every rank's buffer, with the ranks
+    played one after another on a single GPU (no kernel waits on another): afterwards every
+    buffer holds the whole product."""
+    import torch
+    m, n, k = 512, 2048, 256
+    a32 = normal((m, k), 40, 1.0 / np.sqrt(k))
+    b32 = normal((k, n), 41, 1.0 / np.sqrt(k))
+    ta, a_up = to_bf16_bits(a32)
+    tb, b_up = to_bf16_bits(b32)
+    da = ta.cuda()
+    db = tb.t().contiguous().cuda()          # [N, K]
+    bufs = [torch.full((m, n), 9.0, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    ptrs = [b.data_ptr() for b in bufs]
+    w = n // world
+    for rank in range(world):
+        sb.matmul_allgather(da, db[rank * w:(rank + 1) * w].contiguous(), ptrs, rank, n, torch.bfloat16)
+    sb.synchronize()
+    want = oracle.matmul(a_up, b_up, 1, 1, 1)
+    for b in bufs:
+        assert rel_err(b.float().cpu().numpy(), want) < BF16_TOL
+    assert all(torch.equal(bufs[0], b) for b in bufs[1:])
+    single = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    sb.matmul(da, db, single, 1, 1, 1, b_layout=sb._lib.LAYOUT_COL_MAJOR).apply()
+    sb.synchronize()
+    assert torch.equal(single, bufs[0])      # sharding changes nothing, bit for bit
