@@ -33,8 +33,8 @@ GEMM_N = 8192
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes (read + write) of one 8192^3 GEMM launch; from the ncu capture summarised in
-# profiles/gemm_tn_kernel_bf16_8192.md (dram__bytes_read.sum + dram__bytes_write.sum).
-GEMM_DRAM_TRAFFIC_BYTES = 1.150e9
+# profiles/gemm_tn_pair_wide_kernel_bf16_8192.md (dram__bytes_read.sum + dram__bytes_write.sum).
+GEMM_DRAM_TRAFFIC_BYTES = 1.040e9
 ORACLE_TILE = (64, 64, 32)  # logical tile of the reference's GEMM example configuration
 # name -> (batch*heads, seq, causal) for attention; None for the f32 GEMM
 SIDE_WORKLOADS = {
@@ -42,6 +42,7 @@ SIDE_WORKLOADS = {
     "attn_fwd_h32_s8192_d128_causal_one_gpu_shard": (32, 8192, True),
     "attn_fwd_b8_h32_s8192_d128_causal": (256, 8192, True),
     "gemm_f32_4096": None,
+    "tileops_hbm": "tileops",
 }
 
 
@@ -224,6 +225,28 @@ def run_side_workload(name, iters, warmup, peaks):
         return s0.elapsed_time(s1) / iters
 
     spec = SIDE_WORKLOADS[name]
+    if spec == "tileops":
+        # HBM-bound tile ops on 2^28 f32 elements (1 GiB per array, far beyond L2); algorithmic
+        # bytes per element: vec_add 12, relu in place 8, row softmax 8, sum-reduce 4, matvec 4.
+        n = 1 << 28
+        x = torch.rand(n, generator=g, device=dev) - 0.5
+        y = torch.rand(n, generator=g, device=dev)
+        z = torch.empty_like(x)
+        out = torch.zeros(1, device=dev)
+        rows, cols = n // 1024, 1024
+        vec = torch.rand(cols, generator=g, device=dev)
+        zr = torch.empty(rows, device=dev)
+        res = {}
+        for op, launcher, bytes_per_elt in [
+            ("vec_add", sb.vec_add(x, y, z, 4), 12), ("relu", sb.relu(z), 8),
+            ("softmax_rows_1024", sb.softmax(x.view(rows, cols), z.view(rows, cols), 1), 8),
+            ("parallel_reduce", sb.parallel_reduce(x, out, 1024), 4),
+            ("matvec_k1024", sb.matvec(x.view(rows, cols), vec, zr, 1, 1), 4),
+        ]:
+            ms = timed(launcher.apply)
+            gbs = n * bytes_per_elt / (ms * 1e-3) / 1e9
+            res[op] = {"ms": ms, "algorithmic_GBps": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
+        return res
     if spec is None:
         af = torch.rand(4096, 4096, generator=g, device=dev) * 2 - 1
         bf = torch.rand(4096, 4096, generator=g, device=dev) * 2 - 1
@@ -444,6 +467,39 @@ def main():
     if p == 1 and not args.no_extras:
         for name in SIDE_WORKLOADS:
             extras[name] = run_side_workload(name, 10 if "b8" in name else 20, 3, peaks)
+
+    if p > 1 and not args.no_extras:
+        # attention shards by batch x head: every rank runs its contiguous slab of the 256
+        # (batch, head) pairs and the slabs are all-gathered (NCCL) straight into final layout
+        bh_total, s_len = 256, 8192
+        h0, hc = sb.sharding.head_slab(bh_total, p, rank)
+        g.manual_seed(100 + rank)
+        q, k, v = [torch.randn(hc, s_len, 128, generator=g, device=dev).to(torch.bfloat16) for _ in range(3)]
+        o_slab = torch.zeros_like(q)
+        o_full = torch.empty(bh_total, s_len, 128, device=dev, dtype=torch.bfloat16)
+        akl = sb.attention(q, k, v, o_slab, 1.0 / 128 ** 0.5, True)
+
+        def attn_step():
+            akl.apply()
+            dist.all_gather_into_tensor(o_full, o_slab)
+
+        for _ in range(3):
+            attn_step()
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(10):
+            attn_step()
+        a1.record()
+        barrier()
+        ams = max_over_ranks(a0.elapsed_time(a1)) / 10
+        afl = 4.0 * bh_total * s_len * s_len * 128 * 0.5
+        atf = afl / (ams * 1e-3) / 1e12
+        extras["attn_fwd_b8_h32_s8192_d128_causal_sharded"] = {
+            "ms": ams, "tflops_whole_job": atf, "per_gpu_tflops": atf / p,
+            "exchange": "NCCL all-gather of the output slabs (rank-major = final [B*H, S, D] layout)"}
+        sb.synchronize()
+        del q, k, v, o_slab, o_full
 
     # ---- roofline of the dominant kernel ---------------------------------------------------------
     timed_region_s = ms_total * 1e-3
