@@ -41,11 +41,12 @@ def lib() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
+    path = os.environ.get("SILE_CUDA_LIBRARY", LIB_PATH)  # an alternative build of the same library
+    if not os.path.exists(path):
         raise RuntimeError(
-            f"{LIB_PATH} is missing: build it with `python -m sile_b200.build` "
+            f"{path} is missing: build it with `python -m sile_b200.build` "
             "(there is no CPU or PyTorch fallback)")
-    L = C.CDLL(LIB_PATH)
+    L = C.CDLL(path)
     ksig = [C.POINTER(C.c_void_p), _i64, _i64, C.POINTER(_i64), _i64]
     for name in EXPORTED_SYMBOLS:
         if name.startswith("sile_kernel_"):
