@@ -1,18 +1,23 @@
 """The CPU oracle against every golden vector the reference's own tests hold
 for this path.  These pin the oracle before any CUDA result is compared to it."""
+import json
+import os
+
 import numpy as np
+
+GOLDEN = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_vectors.json")))
 
 
 def test_matmul_4x4_golden(oracle):
     # crates/sile/tests/backend_matmul.rs:29-64 and llvm_ir_cpu_runtime.rs:53-95
-    a = np.arange(1, 17, dtype=np.float32).reshape(4, 4)
-    b = np.array([1, 0, 2, 1, 0, 1, 3, 2, 1, 0, 4, 3, 0, 1, 5, 4], np.float32).reshape(4, 4)
+    g = GOLDEN["matmul_4x4"]
+    a = np.array(g["a"], np.float32).reshape(4, 4)
+    b = np.array(g["b"], np.float32).reshape(4, 4)
     c = np.zeros((4, 4), np.float32)
-    oracle.lib.sile_oracle_bind_matmul(2, 2, 2)
-    oracle.launch("matmul", [a, b, c], grid=(4, 1, 1))
-    expected = np.array([4, 6, 40, 30, 12, 14, 96, 70, 20, 22, 152, 110, 28, 30, 208, 150],
-                        np.float32)
-    assert np.abs(c.ravel() - expected).max() < 1e-4
+    oracle.lib.sile_oracle_bind_matmul(*g["tile"])
+    oracle.launch("matmul", [a, b, c], grid=tuple(g["grid"]))
+    expected = np.array(g["expected"], np.float32)
+    assert np.abs(c.ravel() - expected).max() < g["tolerance_abs"]
     # backend_metal.rs:69-105 asserts the same values exactly
     assert (c.ravel() == expected).all()
 
@@ -59,9 +64,10 @@ def test_vec_add_golden(oracle):
 
 def test_relu_golden(oracle):
     # crates/sile/tests/llvm_ir_cpu_runtime.rs:118-140
-    x = np.array([-3.0, -1.0, 0.0, 2.5, 4.0, -7.0, 8.0, -0.5], np.float32)
+    g = GOLDEN["relu_8"]
+    x = np.array(g["x"], np.float32)
     oracle.launch("relu", [x], grid=(1, 1, 1))
-    assert (x == np.array([0, 0, 0, 2.5, 4.0, 0, 8.0, 0], np.float32)).all()
+    assert (x == np.array(g["expected"], np.float32)).all()
 
 
 def test_softmax_rows_sum_to_one(oracle):
