@@ -307,6 +307,81 @@ int read_and_clear_status() {
   return SILE_OK;
 }
 
+// Large 16-bit matmuls from host memory: A travels in row chunks on one stream, each chunk's
+// GEMM runs on a second as soon as its rows (and all of B) have arrived, and its rows of C return
+// on a third, so the two PCIe directions and the tensor cores work at the same time.  Only for
+// launches that write every element of C (whole logical tiles, full grid), where chunking the
+// rows cannot change which elements are written.
+int launch_host_matmul_pipelined(const SileKernelDesc* d, void* const* host, const int64_t* shapes, bool* handled) {
+  *handled = false;
+  const int64_t m = shapes[0], k = shapes[1], n = shapes[5];
+  const int64_t bm = const_or_one(d, 0);
+  if (d->in_dtype == SILE_DTYPE_F32 || d->b_layout != SILE_LAYOUT_COL_MAJOR) return SILE_OK;
+  int64_t rows = 1024;
+  while (rows % bm != 0 && rows < m) rows += 1024;   // chunk boundaries must fall on logical tile boundaries
+  if (m < 4 * rows || rows % bm != 0 || m % bm != 0 || static_cast<double>(m) * n * k < 1e11) return SILE_OK;
+  *handled = true;
+  const size_t in_sz = dtype_size(d->in_dtype), out_sz = dtype_size(d->out_dtype);
+  cudaStream_t s_in = nullptr, s_run = nullptr, s_out = nullptr;
+  SILE_CUDA_TRY(cudaStreamCreateWithFlags(&s_in, cudaStreamNonBlocking));
+  SILE_CUDA_TRY(cudaStreamCreateWithFlags(&s_run, cudaStreamNonBlocking));
+  SILE_CUDA_TRY(cudaStreamCreateWithFlags(&s_out, cudaStreamNonBlocking));
+  void *da = nullptr, *db = nullptr, *dc = nullptr;
+  std::vector<cudaEvent_t> events;
+  int rc = SILE_OK;
+  auto check = [&](cudaError_t e, const char* what) {
+    if (e != cudaSuccess && rc == SILE_OK) rc = fail(SILE_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+    return e == cudaSuccess;
+  };
+  auto new_event = [&]() {
+    cudaEvent_t ev = nullptr;
+    check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
+    events.push_back(ev);
+    return ev;
+  };
+  check(cudaMallocAsync(&da, static_cast<size_t>(m * k) * in_sz, s_in), "device allocation");
+  check(cudaMallocAsync(&db, static_cast<size_t>(k * n) * in_sz, s_in), "device allocation");
+  check(cudaMallocAsync(&dc, static_cast<size_t>(m * n) * out_sz, s_in), "device allocation");
+  if (rc == SILE_OK) {
+    check(cudaMemcpyAsync(db, host[1], static_cast<size_t>(k * n) * in_sz, cudaMemcpyHostToDevice, s_in), "host->device copy");
+    for (int64_t r0 = 0; r0 < m && rc == SILE_OK; r0 += rows) {
+      const int64_t rc_rows = std::min(rows, m - r0);
+      const size_t a_off = static_cast<size_t>(r0 * k) * in_sz, c_off = static_cast<size_t>(r0 * n) * out_sz;
+      check(cudaMemcpyAsync(static_cast<char*>(da) + a_off, static_cast<const char*>(host[0]) + a_off,
+                            static_cast<size_t>(rc_rows * k) * in_sz, cudaMemcpyHostToDevice, s_in), "host->device copy");
+      cudaEvent_t arrived = new_event();
+      check(cudaEventRecord(arrived, s_in), "cudaEventRecord");
+      check(cudaStreamWaitEvent(s_run, arrived, 0), "cudaStreamWaitEvent");
+      if (rc != SILE_OK) break;
+      GemmProblem p;
+      p.a = static_cast<char*>(da) + a_off; p.b = db; p.c = static_cast<char*>(dc) + c_off;
+      p.m = rc_rows; p.n = n; p.k = k;
+      p.in_dtype = d->in_dtype; p.out_dtype = d->out_dtype; p.b_layout = d->b_layout;
+      p.bm = bm; p.bn = const_or_one(d, 1); p.bk = const_or_one(d, 2);
+      rc = gemm_launch(p, s_run);
+      if (rc != SILE_OK) break;
+      cudaEvent_t computed = new_event();
+      check(cudaEventRecord(computed, s_run), "cudaEventRecord");
+      check(cudaStreamWaitEvent(s_out, computed, 0), "cudaStreamWaitEvent");
+      check(cudaMemcpyAsync(static_cast<char*>(host[2]) + c_off, static_cast<char*>(dc) + c_off,
+                            static_cast<size_t>(rc_rows * n) * out_sz, cudaMemcpyDeviceToHost, s_out), "device->host copy");
+    }
+  }
+  check(cudaStreamSynchronize(s_in), "host->device copy");
+  check(cudaStreamSynchronize(s_run), "kernel execution");
+  check(cudaStreamSynchronize(s_out), "device->host copy");
+  if (rc == SILE_OK) rc = read_and_clear_status();
+  for (void* ptr : {da, db, dc})
+    if (ptr) cudaFreeAsync(ptr, s_in);
+  cudaStreamSynchronize(s_in);
+  for (cudaEvent_t ev : events)
+    if (ev) cudaEventDestroy(ev);
+  cudaStreamDestroy(s_in);
+  cudaStreamDestroy(s_run);
+  cudaStreamDestroy(s_out);
+  return rc;
+}
+
 int launch_host(const SileKernelDesc* d, void* const* host, const int64_t* shapes, int64_t ns, int64_t ntg) {
   if (int rc = validate_desc(d)) return rc;
   if (int rc = check_device()) return rc;
@@ -323,6 +398,14 @@ int launch_host(const SileKernelDesc* d, void* const* host, const int64_t* shape
     uint64_t keep = UINT64_MAX;
     SILE_CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
     pool_dev = cur_dev;
+  }
+  if (d->op == SILE_OP_MATMUL && !args[2].is_input && host[0] && host[1] && host[2]) {
+    bool handled = false;
+    const int rc = launch_host_matmul_pipelined(d, host, shapes, &handled);
+    if (handled) {
+      if (rc == SILE_OK) t_last_status = SILE_OK;
+      return rc;
+    }
   }
   cudaStream_t stream = nullptr;
   SILE_CUDA_TRY(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));

@@ -233,3 +233,47 @@ def test_fused_allgather_epilogue_on_one_gpu(sb, oracle, world):
     sb.matmul(da, db, single, 1, 1, 1, b_layout=sb._lib.LAYOUT_COL_MAJOR).apply()
     sb.synchronize()
     assert torch.equal(single, bufs[0])      # sharding changes nothing, bit for bit
+
+
+def test_host_buffer_launch_pipelines_large_bf16_and_matches_device_launch(sb):
+    """sile_cuda_launch_host streams a large 16-bit matmul in row chunks (copy in / compute /
+    copy out overlapped); the result must equal the device-resident launch bit for bit."""
+    import torch
+    m, n, k = 4096, 4096, 8192
+    g = torch.Generator().manual_seed(3)
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).to(torch.bfloat16).pin_memory()
+    b = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16).pin_memory()  # [N, K]: column-major B
+    c_host = torch.zeros(m, n, dtype=torch.bfloat16).pin_memory()
+
+    class _KN:
+        shape = (k, n)
+
+        @staticmethod
+        def data_ptr():
+            return b.data_ptr()
+
+    desc = sb.make_desc(sb._lib.OP_MATMUL, sb._lib.DTYPE_BF16, sb._lib.DTYPE_BF16, sb._lib.LAYOUT_COL_MAJOR, consts=(64, 64, 32))
+    sb.KernelLauncher(desc, [a, _KN, c_host]).grid((m // 64, n // 64, 1)).apply_host()
+    c_dev = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    sb.matmul(a.cuda(), b.cuda(), c_dev, 64, 64, 32, b_layout=sb._lib.LAYOUT_COL_MAJOR).apply()
+    sb.synchronize()
+    assert torch.equal(c_host, c_dev.cpu())
+    ref = a[:256].float() @ b.float().t()
+    assert rel_err(c_host[:256].float().numpy(), ref.numpy()) < BF16_TOL
+
+
+@pytest.mark.parametrize("kernel", ["single", "wide"])
+def test_f16_inputs_and_outputs(sb, kernel, monkeypatch):
+    """fp16 operands (kind::f16 with the f16 input format) and fp16 / f32 outputs."""
+    import torch
+    monkeypatch.setenv("SILE_CUDA_GEMM_KERNEL", kernel)
+    m, n, k = 512, 1024, 384
+    g = torch.Generator().manual_seed(9)
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).to(torch.float16)
+    b = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.float16)      # [N, K]
+    want = (a.double() @ b.double().t()).numpy()
+    for out_dtype, tol in ((torch.float16, 2e-3), (torch.float32, 1e-5)):
+        c = torch.zeros(m, n, device="cuda", dtype=out_dtype)
+        sb.matmul(a.cuda(), b.cuda(), c, 1, 1, 1, b_layout=sb._lib.LAYOUT_COL_MAJOR).apply()
+        sb.synchronize()
+        assert rel_err(c.double().cpu().numpy(), want) < tol
