@@ -10,17 +10,22 @@
 // One CTA = one (batch*head, 256-query block) = two 128-row Q tiles, 12 warps:
 //   warp 0        TMA producer: Q tiles once, then K_j / V_j through 2-stage rings
 //   warp 1        MMA issuer:   S_t = Q_t K_j^T (smem x smem) and O_t += P_t V_j
-//                 (P_t read from TMEM, V_j MN-major from smem), f32 accumulators in TMEM
+//                 (P_t read from TMEM, V_j MN-major from smem), f32 accumulators in TMEM.
+//                 The tiles are served in a fixed order (PV0 S0' PV1 S1' ...), which keeps their
+//                 softmax phases apart; one issuing warp per tile was measured ~17 % slower
+//                 because the tiles then fall into step and their softmaxes collide.
 //   warps 4..7    softmax of Q tile 0 (thread r owns row r = TMEM lane r)
 //   warps 8..11   softmax of Q tile 1
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 columns each; P_t (bf16 pairs) overwrites the
-// first 64 columns of S_t.  The issue order S0 S1 | PV0 S0' PV1 S1' ... lets the softmax of one
-// tile run under the MMAs of the other.  O is rescaled only when the row max has grown by more
+// first 64 columns of S_t.  Per tile the chain is S -> softmax -> PV -> next S; the softmax of one
+// tile runs under the MMAs of the other.  O is rescaled only when the row max has grown by more
 // than 2^8 since the last rescale; the same (stale) max is used for P and l, so the result is
 // unchanged.  The rescale and the final 1/l normalisation are done by the softmax warps.
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 #include "internal.h"
 #include "ptx.cuh"
@@ -55,9 +60,14 @@ struct AttnParams {
   int64_t row_stride;  // elements between consecutive rows of O (= D)
 };
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));  // volatile: keeps the staged order below
   return y;
 }
 
@@ -156,22 +166,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0 && n_max > 0) {
+    // The whole warp runs this loop (waits included) and only the tcgen05 instructions are
+    // predicated on one elected lane: see umma_ss_f16_if.
+    if (n_max > 0) {
       constexpr uint32_t idesc_s = make_idesc_f16(kTileQ, kBlockKV, true, false, false);  // Q K^T: both K-major
       constexpr uint32_t idesc_o = make_idesc_f16(kTileQ, kD, true, false, true);         // P V: V is MN-major
       const uint32_t q_addr = smem_u32(smem + kSmemQ);
       const uint32_t k_addr = smem_u32(smem + kSmemK);
       const uint32_t v_addr = smem_u32(smem + kSmemV);
+      const uint32_t el = elect_one() ? 1u : 0u;
       bool ok = true;
 
       // Descriptors are built once; inside the unrolled loops only a constant is added to the
-      // 14-bit start-address field, so issuing one MMA costs a handful of instructions (a
-      // 128 x 128 x 16 MMA runs for 64 cycles: anything slower than that starves the tensor pipe).
+      // 14-bit start-address field (a 128 x 128 x 16 MMA runs for 64 cycles: an issue sequence
+      // slower than that starves the tensor pipe).
       const uint64_t q_desc[2] = {make_smem_desc_sw128(q_addr, 16, 1024), make_smem_desc_sw128(q_addr + kTileBytes, 16, 1024)};
       const uint64_t k_desc[2] = {make_smem_desc_sw128(k_addr, 16, 1024), make_smem_desc_sw128(k_addr + kTileBytes, 16, 1024)};
       const uint64_t v_desc[2] = {make_smem_desc_sw128(v_addr, kPanelBytes, 1024),
                                   make_smem_desc_sw128(v_addr + kTileBytes, kPanelBytes, 1024)};
-
+      auto wait = [&](uint64_t* bar, uint32_t parity) {
+        const bool w = mbar_wait(bar, parity, status, SILE_ERR_TIMEOUT);
+        return __all_sync(0xffffffffu, w);
+      };
       auto issue_s = [&](int t, int st) {
         // S_t = Q_t (128 x 128, two 64-wide k panels) * K_st^T
         const uint64_t da = q_desc[t], db = k_desc[st];
@@ -180,59 +196,59 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         for (int kk = 0; kk < kD / 16; ++kk) {
           constexpr int kPanelUnits = kPanelBytes >> 4;
           const uint32_t off = (kk >> 2) * kPanelUnits + (kk & 3) * 2;  // in 16-byte units
-          umma_ss_f16<1>(d, da + off, db + off, idesc_s, kk != 0 ? 1u : 0u);
+          umma_ss_f16_if<1>(el, d, da + off, db + off, idesc_s, kk != 0 ? 1u : 0u);
         }
-        umma_commit<1>(&s_full[t]);
+        umma_commit_if<1>(el, smem_u32(&s_full[t]));
       };
-      auto issue_pv = [&](int t, int st, bool accumulate) {
+      auto issue_pv = [&](int t, int st, bool accumulate, bool last) {
         // O_t += P_t (TMEM, 8 columns per 16 keys) * V_st (rows = keys, 2048 B per 16 keys; d panels 16 KiB apart)
         const uint64_t db = v_desc[st];
         const uint32_t d = tmem_o[t], a = tmem_s[t];
-        umma_ts_f16(d, a, db, idesc_o, accumulate ? 1u : 0u);
+        umma_ts_f16_if<1>(el, d, a, db, idesc_o, accumulate ? 1u : 0u);
 #pragma unroll
-        for (int kk = 1; kk < kBlockKV / 16; ++kk) umma_ts_f16(d, a + kk * 8, db + kk * 128, idesc_o, 1u);
-        umma_commit<1>(&o_done[t]);
+        for (int kk = 1; kk < kBlockKV / 16; ++kk) umma_ts_f16_if<1>(el, d, a + kk * 8, db + kk * 128, idesc_o, 1u);
+        if (last) umma_commit_if<1>(el, smem_u32(&o_done[t]));  // only the epilogue waits for O; see the rescale comment below
       };
 
       // prologue: S_0 for both tiles
-      if (n_kv[0] > 0) ok = ok && mbar_wait(&q_full[0], 0, status, SILE_ERR_TIMEOUT);
-      ok = ok && mbar_wait(&k_full[0], 0, status, SILE_ERR_TIMEOUT);
+      if (n_kv[0] > 0) ok = ok && wait(&q_full[0], 0);
+      ok = ok && wait(&k_full[0], 0);
       if (ok) {
         tcgen05_fence_after();
         if (n_kv[0] > 0) issue_s(0, 0);
         if (n_kv[1] > 0) {
-          ok = mbar_wait(&q_full[1], 0, status, SILE_ERR_TIMEOUT);
+          ok = wait(&q_full[1], 0);
           if (ok) {
             tcgen05_fence_after();
             issue_s(1, 0);
           }
         }
-        umma_commit<1>(&k_empty[0]);
+        umma_commit_if<1>(el, smem_u32(&k_empty[0]));
       }
       for (int j = 0; j < n_max && ok; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int st_n = (j + 1) & 1;
         const uint32_t ph_n = ((j + 1) >> 1) & 1;
-        if (!mbar_wait(&v_full[st], ph, status, SILE_ERR_TIMEOUT)) { ok = false; break; }
+        if (!wait(&v_full[st], ph)) { ok = false; break; }
         if (j < n_kv[0]) {
-          if (!mbar_wait(&p_full[0], j & 1, status, SILE_ERR_TIMEOUT)) { ok = false; break; }
+          if (!wait(&p_full[0], j & 1)) { ok = false; break; }
           tcgen05_fence_after();
-          issue_pv(0, st, j > 0);
+          issue_pv(0, st, j > 0, j + 1 == n_kv[0]);
         }
         if (j + 1 < n_max) {
-          if (!mbar_wait(&k_full[st_n], ph_n, status, SILE_ERR_TIMEOUT)) { ok = false; break; }
+          if (!wait(&k_full[st_n], ph_n)) { ok = false; break; }
           tcgen05_fence_after();
         }
         if (j + 1 < n_kv[0]) issue_s(0, st_n);
         if (j < n_kv[1]) {
-          if (!mbar_wait(&p_full[1], j & 1, status, SILE_ERR_TIMEOUT)) { ok = false; break; }
+          if (!wait(&p_full[1], j & 1)) { ok = false; break; }
           tcgen05_fence_after();
-          issue_pv(1, st, j > 0);
+          issue_pv(1, st, j > 0, j + 1 == n_kv[1]);
         }
-        umma_commit<1>(&v_empty[st]);
+        umma_commit_if<1>(el, smem_u32(&v_empty[st]));
         if (j + 1 < n_kv[1]) issue_s(1, st_n);
-        if (j + 1 < n_max) umma_commit<1>(&k_empty[st_n]);
+        if (j + 1 < n_max) umma_commit_if<1>(el, smem_u32(&k_empty[st_n]));
       }
     }
     __syncwarp();
@@ -272,15 +288,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
             if (kv0 + c * 32 + i > limit) sr[c][i] = 0xff800000u;  // -inf
       }
 
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      float mx[8];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        mx0 = fmaxf(mx0, __uint_as_float(sr[0][i]));
-        mx1 = fmaxf(mx1, __uint_as_float(sr[1][i]));
-        mx2 = fmaxf(mx2, __uint_as_float(sr[2][i]));
-        mx3 = fmaxf(mx3, __uint_as_float(sr[3][i]));
+      for (int c = 0; c < 8; ++c) mx[c] = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          mx[2 * c] = max3(mx[2 * c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+          mx[2 * c + 1] = max3(mx[2 * c + 1], __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+        }
       }
-      const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      const float m_blk = fmaxf(max3(mx[0], mx[1], mx[2]), max3(max3(mx[3], mx[4], mx[5]), mx[6], mx[7])) * p.scale_log2;
       const float m_new = fmaxf(m_used, m_blk);
       const bool rescale = (m_new - m_used > kRescaleThreshold) || (m_used == -INFINITY);  // NaN-safe: inf - (-inf)
       float alpha = 1.0f;
@@ -291,12 +310,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       const float m_sub = (m_used == -INFINITY) ? 0.0f : m_used;
 
       if (j > 0 && __any_sync(0xffffffffu, rescale)) {
-        // O_t of block j-1 is complete whenever S_t of block j is (MMAs retire in issue order);
-        // the wait gives the tcgen05 -> thread ordering for the accumulator.
-        if (!mbar_wait(&o_done[t], (j - 1) & 1, status, SILE_ERR_TIMEOUT)) ok = false;
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tcgen05_fence_after();
+        // O_t already holds block j-1: S_t of block j was issued after P_{j-1} V_{j-1}, MMAs
+        // retire in issue order, and the s_full wait above ordered this thread after all of them.
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t orow[32];
@@ -309,20 +324,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         tcgen05_wait_st();
       }
 
-      float sum0 = 0.0f, sum1 = 0.0f;
+      // P = 2^(s * scale_log2 - m), staged per 32-key chunk so that its 32 MUFU ops are independent
+      // and issue back to back (FMA -> MUFU -> ADD per element leaves the warp waiting on MUFU
+      // latency between elements).
+      float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sr[c][i] = __float_as_uint(fmaf(__uint_as_float(sr[c][i]), p.scale_log2, -m_sub));
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sr[c][i] = __float_as_uint(ex2(__uint_as_float(sr[c][i])));
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2(fmaf(__uint_as_float(sr[c][2 * i]), p.scale_log2, -m_sub));
-          const float p1 = ex2(fmaf(__uint_as_float(sr[c][2 * i + 1]), p.scale_log2, -m_sub));
-          sum0 += p0;
-          sum1 += p1;
-          pk[i] = pack_bf16x2(p0, p1);
+        for (int i = 0; i < 8; ++i) {
+          const float p0 = __uint_as_float(sr[c][4 * i]), p1 = __uint_as_float(sr[c][4 * i + 1]);
+          const float p2 = __uint_as_float(sr[c][4 * i + 2]), p3 = __uint_as_float(sr[c][4 * i + 3]);
+          sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+          pk[2 * i] = pack_bf16x2(p0, p1);
+          pk[2 * i + 1] = pack_bf16x2(p2, p3);
         }
         tmem_st_32x32b_x16(ts + c * 16, pk);
       }
+      sum0 += sum2;
+      sum1 += sum3;
       l = l * alpha + (sum0 + sum1);
       tcgen05_wait_st();
       tcgen05_fence_before();
@@ -330,7 +354,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     }
 
     if (ok && n > 0) {
-      if (!mbar_wait(&o_done[t], (n - 1) & 1, status, SILE_ERR_TIMEOUT)) ok = false;
+      if (!mbar_wait(&o_done[t], 0, status, SILE_ERR_TIMEOUT)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tcgen05_fence_after();
@@ -381,6 +405,12 @@ int attention_launch(const AttnProblem& a, cudaStream_t stream) {
   for (const void* ptr : {a.q, a.k, a.v, static_cast<const void*>(a.o)})
     if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(SILE_ERR_UNSUPPORTED, "attention: buffers must be 16-byte aligned");
   if (!(a.scale > 0.0f)) return fail(SILE_ERR_INVALID, "attention: scale must be positive");
+
+  // SILE_CUDA_ATTN_KERNEL=pair selects the CTA-pair kernel (attn_pair_sm100.cu): half the K / V
+  // traffic per SM and a deeper ring, but twice the tcgen05.commit instructions and cross-CTA
+  // hand-offs; measured ~12 % slower than this file's kernel, which stays the default.
+  const char* which = std::getenv("SILE_CUDA_ATTN_KERNEL");
+  if (which && std::strcmp(which, "pair") == 0) return attention_pair_launch(a, stream);
 
   int* status = nullptr;
   if (int rc = device_status_word(&status)) return rc;

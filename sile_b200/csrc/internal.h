@@ -72,6 +72,8 @@ struct AttnProblem {
   int causal = 0;
 };
 int attention_launch(const AttnProblem& p, cudaStream_t stream);
+// CTA-pair kernel; arguments already validated by attention_launch.
+int attention_pair_launch(const AttnProblem& p, cudaStream_t stream);
 
 // ---- standalone tile ops (HBM-bound) --------------------------------------------
 int vec_add_launch(const float* a, const float* b, float* c, int64_t n, cudaStream_t stream);

@@ -20,6 +20,13 @@ def sb():
     return sile_b200
 
 
+@pytest.fixture(params=["single", "pair"], autouse=True)
+def attn_kernel(request, monkeypatch):
+    """Every case runs on both kernels: the one-CTA default and the CTA-pair (cta_group::2) one."""
+    monkeypatch.setenv("SILE_CUDA_ATTN_KERNEL", request.param)
+    return request.param
+
+
 def _inputs(bh, s, d, seed):
     import torch
     g = torch.Generator(device="cuda").manual_seed(seed)
