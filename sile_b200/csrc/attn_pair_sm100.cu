@@ -66,7 +66,7 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 }
 __device__ __forceinline__ float ex2(float x) {
   float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));  // volatile: keeps the staged order below
   return y;
 }
 
@@ -80,9 +80,9 @@ __device__ __forceinline__ int kv_blocks_for_rows(const PairParams& p, int q0) {
   return min(all, last_q / kBlockKV + 1);
 }
 
-__device__ __forceinline__ void commit_both(uint64_t* bar) {
-  umma_commit_pair_to(bar, 0);
-  umma_commit_pair_to(bar, 1);
+__device__ __forceinline__ void commit_both(uint32_t elected, uint64_t* bar) {
+  umma_commit_if<2>(elected, pair_addr(bar, 0));
+  umma_commit_if<2>(elected, pair_addr(bar, 1));
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -196,7 +196,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
-    if (leader && lane == 0 && n_max > 0) {
+    // The whole warp runs this loop and only the tcgen05 instructions are predicated on one
+    // elected lane: see umma_ss_f16_if.
+    if (leader && n_max > 0) {
+      const uint32_t el = elect_one() ? 1u : 0u;
+      auto wait = [&](uint64_t* bar, uint32_t parity, int site) {
+        const bool w = mbar_wait<true>(bar, parity, status, SILE_ERR_TIMEOUT, site);
+        return __all_sync(0xffffffffu, w);
+      };
       constexpr uint32_t idesc_s = make_idesc_f16(kPairQ, kBlockKV, true, false, false);  // Q K^T: both K-major
       constexpr uint32_t idesc_o = make_idesc_f16(kPairQ, kD, true, false, true);         // P V: V is MN-major
       bool ok = true;
@@ -216,56 +223,56 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         for (int kk = 0; kk < kD / 16; ++kk) {
           const uint32_t off_q = (kk >> 2) * (kQPanelBytes >> 4) + (kk & 3) * 2;  // in 16-byte units
           const uint32_t off_k = (kk >> 2) * (kKPanelBytes >> 4) + (kk & 3) * 2;
-          umma_ss_f16<2>(d, da + off_q, db + off_k, idesc_s, kk != 0 ? 1u : 0u);
+          umma_ss_f16_if<2>(el, d, da + off_q, db + off_k, idesc_s, kk != 0 ? 1u : 0u);
         }
-        commit_both(&s_full[t]);
+        commit_both(el, &s_full[t]);
       };
       auto issue_pv = [&](int t, int j, bool accumulate, bool last) {
         // O_t (256 x 128 d) += P_t (TMEM, 8 columns per 16 keys) * V_j (rows = keys, 2048 B per
         // 16 keys), 64 head-dim columns from each CTA
         const uint64_t db = v_desc0 + (j % kStagesV) * (kVStageBytes >> 4);
         const uint32_t d = tmem_o[t], a = tmem_s[t];
-        umma_ts_f16<2>(d, a, db, idesc_o, accumulate ? 1u : 0u);
+        umma_ts_f16_if<2>(el, d, a, db, idesc_o, accumulate ? 1u : 0u);
 #pragma unroll
-        for (int kk = 1; kk < kBlockKV / 16; ++kk) umma_ts_f16<2>(d, a + kk * 8, db + kk * 128, idesc_o, 1u);
-        if (last) commit_both(&o_done[t]);  // only the epilogue waits for O; see the rescale comment below
+        for (int kk = 1; kk < kBlockKV / 16; ++kk) umma_ts_f16_if<2>(el, d, a + kk * 8, db + kk * 128, idesc_o, 1u);
+        if (last) commit_both(el, &o_done[t]);  // only the epilogue waits for O; see the rescale comment below
       };
 
       // prologue: S_0 for both tiles
-      if (n_kv[0] > 0) ok = ok && mbar_wait<true>(&q_full[0], 0, status, SILE_ERR_TIMEOUT, 3);
-      ok = ok && mbar_wait<true>(&k_full[0], 0, status, SILE_ERR_TIMEOUT, 4);
+      if (n_kv[0] > 0) ok = ok && wait(&q_full[0], 0, 3);
+      ok = ok && wait(&k_full[0], 0, 4);
       if (ok) {
         tcgen05_fence_after();
         if (n_kv[0] > 0) issue_s(0, 0);
         if (n_kv[1] > 0) {
-          ok = mbar_wait<true>(&q_full[1], 0, status, SILE_ERR_TIMEOUT, 3);
+          ok = wait(&q_full[1], 0, 3);
           if (ok) {
             tcgen05_fence_after();
             issue_s(1, 0);
           }
         }
-        commit_both(&k_empty[0]);
+        commit_both(el, &k_empty[0]);
       }
       for (int j = 0; j < n_max && ok; ++j) {
-        if (!mbar_wait<true>(&v_full[j % kStagesV], (j / kStagesV) & 1, status, SILE_ERR_TIMEOUT, 5)) { ok = false; break; }
+        if (!wait(&v_full[j % kStagesV], (j / kStagesV) & 1, 5)) { ok = false; break; }
         if (j < n_kv[0]) {
-          if (!mbar_wait<true>(&p_full[0], j & 1, status, SILE_ERR_TIMEOUT, 6)) { ok = false; break; }
+          if (!wait(&p_full[0], j & 1, 6)) { ok = false; break; }
           tcgen05_fence_after();
           issue_pv(0, j, j > 0, j + 1 == n_kv[0]);
         }
         if (j + 1 < n_max) {
-          if (!mbar_wait<true>(&k_full[(j + 1) % kStagesK], ((j + 1) / kStagesK) & 1, status, SILE_ERR_TIMEOUT, 4)) { ok = false; break; }
+          if (!wait(&k_full[(j + 1) % kStagesK], ((j + 1) / kStagesK) & 1, 4)) { ok = false; break; }
           tcgen05_fence_after();
         }
         if (j + 1 < n_kv[0]) issue_s(0, j + 1);
         if (j < n_kv[1]) {
-          if (!mbar_wait<true>(&p_full[1], j & 1, status, SILE_ERR_TIMEOUT, 6)) { ok = false; break; }
+          if (!wait(&p_full[1], j & 1, 6)) { ok = false; break; }
           tcgen05_fence_after();
           issue_pv(1, j, j > 0, j + 1 == n_kv[1]);
         }
-        commit_both(&v_empty[j % kStagesV]);
+        commit_both(el, &v_empty[j % kStagesV]);
         if (j + 1 < n_kv[1]) issue_s(1, j + 1);
-        if (j + 1 < n_max) commit_both(&k_empty[(j + 1) % kStagesK]);
+        if (j + 1 < n_max) commit_both(el, &k_empty[(j + 1) % kStagesK]);
       }
     }
     __syncwarp();
@@ -342,20 +349,29 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         tcgen05_wait_st();
       }
 
-      float sum0 = 0.0f, sum1 = 0.0f;
+      // P = 2^(s * scale_log2 - m), staged per 32-key chunk so that its 32 MUFU ops are independent
+      // and issue back to back (FMA -> MUFU -> ADD per element leaves the warp waiting on MUFU
+      // latency between elements).
+      float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sr[c][i] = __float_as_uint(fmaf(__uint_as_float(sr[c][i]), p.scale_log2, -m_sub));
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sr[c][i] = __float_as_uint(ex2(__uint_as_float(sr[c][i])));
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2(fmaf(__uint_as_float(sr[c][2 * i]), p.scale_log2, -m_sub));
-          const float p1 = ex2(fmaf(__uint_as_float(sr[c][2 * i + 1]), p.scale_log2, -m_sub));
-          sum0 += p0;
-          sum1 += p1;
-          pk[i] = pack_bf16x2(p0, p1);
+        for (int i = 0; i < 8; ++i) {
+          const float p0 = __uint_as_float(sr[c][4 * i]), p1 = __uint_as_float(sr[c][4 * i + 1]);
+          const float p2 = __uint_as_float(sr[c][4 * i + 2]), p3 = __uint_as_float(sr[c][4 * i + 3]);
+          sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+          pk[2 * i] = pack_bf16x2(p0, p1);
+          pk[2 * i + 1] = pack_bf16x2(p2, p3);
         }
         tmem_st_32x32b_x16(ts + c * 16, pk);
       }
+      sum0 += sum2;
+      sum1 += sum3;
       l = l * alpha + (sum0 + sum1);
       tcgen05_wait_st();
       tcgen05_fence_before();

@@ -211,7 +211,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // The whole warp runs the loop; the tcgen05 instructions are predicated on one elected lane
+    // (see umma_ss_f16_if), which keeps descriptor arithmetic in the uniform datapath.
+    {
+      const uint32_t el = elect_one() ? 1u : 0u;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -219,11 +222,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(&tmem_empty_bar[buf], acc_phase ^ 1u, status, SILE_ERR_TIMEOUT)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&tmem_empty_bar[buf], acc_phase ^ 1u, status, SILE_ERR_TIMEOUT))) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + buf * kBN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, status, SILE_ERR_TIMEOUT)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, status, SILE_ERR_TIMEOUT))) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t sa = smem_u32(smem + stage * kStageBytes);
           const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
@@ -231,12 +234,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             // +32 bytes per 16-element k step inside the 128-byte swizzle row (address field is >>4)
-            umma_ss_f16<1>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_ss_f16_if<1>(el, tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit<1>(&empty_bar[stage]);
+          umma_commit_if<1>(el, smem_u32(&empty_bar[stage]));
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit<1>(&tmem_full_bar[buf]);
+        if (ok) umma_commit_if<1>(el, smem_u32(&tmem_full_bar[buf]));
       }
     }
     __syncwarp();
@@ -385,7 +388,9 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
-    if (leader && lane == 0) {
+    // Whole warp, predicated tcgen05 instructions: see umma_ss_f16_if.
+    if (leader) {
+      const uint32_t el = elect_one() ? 1u : 0u;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -393,24 +398,24 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait<true>(&tmem_empty_bar[buf], acc_phase ^ 1u, status, SILE_ERR_TIMEOUT, 2)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait<true>(&tmem_empty_bar[buf], acc_phase ^ 1u, status, SILE_ERR_TIMEOUT, 2))) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + buf * kBN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait<true>(&full_bar[stage], phase, status, SILE_ERR_TIMEOUT, 3)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait<true>(&full_bar[stage], phase, status, SILE_ERR_TIMEOUT, 3))) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
           const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
           const uint64_t bdesc = make_smem_desc_sw128(sa + kPairABytes, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) umma_ss_f16<2>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-          umma_commit_pair_to(&empty_bar[stage], 0);
-          umma_commit_pair_to(&empty_bar[stage], 1);
+          for (int k = 0; k < kBK / 16; ++k) umma_ss_f16_if<2>(el, tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_if<2>(el, pair_addr(&empty_bar[stage], 0));
+          umma_commit_if<2>(el, pair_addr(&empty_bar[stage], 1));
           if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
         }
         if (ok) {
-          umma_commit_pair_to(&tmem_full_bar[buf], 0);
-          umma_commit_pair_to(&tmem_full_bar[buf], 1);
+          umma_commit_if<2>(el, pair_addr(&tmem_full_bar[buf], 0));
+          umma_commit_if<2>(el, pair_addr(&tmem_full_bar[buf], 1));
         }
       }
     }
@@ -566,7 +571,10 @@ gemm_tn_pair_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
-    if (leader && lane == 0) {
+    // The whole warp runs the loop; the tcgen05 instructions are predicated on one elected lane
+    // (see umma_ss_f16_if), which keeps descriptor arithmetic in the uniform datapath.
+    if (leader) {
+      const uint32_t el = elect_one() ? 1u : 0u;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -574,7 +582,7 @@ gemm_tn_pair_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
         const uint32_t tile_phase = it & 1;
         for (int kb = 0; kb < num_kb && ok; ++kb) {
-          if (!mbar_wait<true>(&full_bar[stage], phase, status, SILE_ERR_TIMEOUT, 3)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait<true>(&full_bar[stage], phase, status, SILE_ERR_TIMEOUT, 3))) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t sa = smem_u32(smem + stage * kWideStageBytes);
           const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
@@ -582,21 +590,21 @@ gemm_tn_pair_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           for (int h = 0; h < 2; ++h) {
             if (kb == 0) {
               // the previous tile's half h must have been drained by both CTAs' epilogue warps
-              if (!mbar_wait<true>(&tmem_empty_bar[h], tile_phase ^ 1u, status, SILE_ERR_TIMEOUT, 2)) { ok = false; break; }
+              if (!__all_sync(0xffffffffu, mbar_wait<true>(&tmem_empty_bar[h], tile_phase ^ 1u, status, SILE_ERR_TIMEOUT, 2))) { ok = false; break; }
               tcgen05_fence_after();
             }
             const uint64_t bdesc = make_smem_desc_sw128(sa + kPairABytes + h * kPairBBytes, 16, 1024);
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k)
-              umma_ss_f16<2>(tmem_base + h * 256, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_ss_f16_if<2>(el, tmem_base + h * 256, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
             if (kb == num_kb - 1) {
-              umma_commit_pair_to(&tmem_full_bar[h], 0);
-              umma_commit_pair_to(&tmem_full_bar[h], 1);
+              umma_commit_if<2>(el, pair_addr(&tmem_full_bar[h], 0));
+              umma_commit_if<2>(el, pair_addr(&tmem_full_bar[h], 1));
             }
           }
           if (!ok) break;
-          umma_commit_pair_to(&empty_bar[stage], 0);
-          umma_commit_pair_to(&empty_bar[stage], 1);
+          umma_commit_if<2>(el, pair_addr(&empty_bar[stage], 0));
+          umma_commit_if<2>(el, pair_addr(&empty_bar[stage], 1));
           if (++stage == kWideStages) { stage = 0; phase ^= 1u; }
         }
       }
