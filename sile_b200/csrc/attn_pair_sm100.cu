@@ -1,19 +1,19 @@
-// Fused attention forward for sm_100a, CTA-pair form: two CTAs of a cluster (two SMs) work on
-// 512 consecutive query rows of one (batch, head) and SHARE every K / V block.
+// Fused attention forward for sm_100a, CTA-pair form: the two CTAs of a cluster (two SMs) take
+// 128 query rows each of one (batch, head) and SHARE every K / V block.
 //
 // Same algorithm and numerics as the single-CTA kernel in attn_sm100.cu (online softmax over
-// 128-key blocks, f32 statistics, lazily rescaled accumulator).  What changes is who holds what:
-//   * each CTA owns two 128-row Q tiles (rows [256 t + 128 r, +128) of the 512, t = tile,
-//     r = CTA rank), their S / P / O in its own tensor memory, and the softmax of those rows;
-//   * of every K block each CTA stages only its 64 keys, of every V block only its 64 of the 128
-//     head-dim columns (16 KiB per block and operand instead of 32 KiB);
-//   * the MMAs are tcgen05 cta_group::2 instructions issued by the leader CTA: S_t (256 x 128) =
-//     [Q_t of CTA0; Q_t of CTA1] K^T takes the N = 128 keys half from each CTA's shared memory,
-//     and O_t += P_t V takes the N = 128 head-dim columns half from each.
-// The pair therefore pulls each K / V byte from L2 once per 512 query rows instead of once per
-// 256: with one CTA per SM the K / V stream (64 KiB per 128 keys per SM) is what the single-CTA
-// kernel waits for; here it is halved and the freed shared memory doubles the ring depth (4 K and
-// 4 V stages), which hides the L2 latency that two stages exposed.
+// 128-key blocks, f32 statistics, lazily rescaled accumulator).  What changes:
+//   * the MMAs are tcgen05 cta_group::2 instructions issued by the leader CTA: S (256 x 128) =
+//     [Q of CTA0; Q of CTA1] K^T takes the N = 128 keys half from each CTA's shared memory, and
+//     O += P V takes the N = 128 head-dim columns half from each.  Of every K block each CTA
+//     stages only its 64 keys, of every V block only its 64 head-dim columns, so the pair pulls
+//     each K / V byte from L2 once per 256 query rows, like the single-CTA kernel, while each SM
+//     holds ONE Q tile;
+//   * with one tile per SM the 512 tensor-memory columns hold THREE S buffers next to O.  The
+//     issue order S0 S1 S2 | PV0 S3 | PV1 S4 | ... puts Q K^T of block j+3 in flight as soon as
+//     P_j has been consumed, so the softmax warps never wait for the tensor core: the step that
+//     bounds the kernel, 128 exp2 per row and block on the 16-lane MUFU pipe, runs back to back
+//     instead of alternating with the tile's own MMAs.
 //
 // No counterpart in the reference: attention there is a composition of tile ops
 // (crates/sile-tile-ir/src/lower.rs:509-748), and the reference has no CUDA backend.
@@ -30,30 +30,30 @@ namespace {
 using namespace ptx;
 
 constexpr int kD = 128;             // head dim
-constexpr int kTileQ = 128;         // rows per Q tile (= TMEM lanes)
-constexpr int kPairQ = 2 * kTileQ;  // rows one cta_group::2 MMA covers (one tile from each CTA)
-constexpr int kClusterQ = 2 * kPairQ;
+constexpr int kTileQ = 128;         // rows per CTA (= TMEM lanes)
+constexpr int kPairQ = 2 * kTileQ;  // rows one cta_group::2 MMA covers
 constexpr int kBlockKV = 128;
+constexpr int kBufS = 3;            // S buffers in tensor memory
 constexpr int kQPanelBytes = kTileQ * 64 * 2;       // [128 rows x 64 d], 128B-swizzled
 constexpr int kQTileBytes = 2 * kQPanelBytes;       // [128 x 128]
 constexpr int kKPanelBytes = (kBlockKV / 2) * 64 * 2;  // this CTA's [64 keys x 64 d]
 constexpr int kKStageBytes = 2 * kKPanelBytes;         // [64 keys x 128 d]
 constexpr int kVStageBytes = kBlockKV * 64 * 2;        // this CTA's [128 keys x 64 d]
-constexpr int kStagesK = 4;
+constexpr int kStagesK = 5;  // S_{j+3} is issued while block j is still in its softmax
 constexpr int kStagesV = 4;
-constexpr int kThreads = 384;
+constexpr int kThreads = 192;
 constexpr int kSmemQ = 0;
-constexpr int kSmemK = kSmemQ + 2 * kQTileBytes;
+constexpr int kSmemK = kSmemQ + kQTileBytes;
 constexpr int kSmemV = kSmemK + kStagesK * kKStageBytes;
 constexpr int kSmemBar = kSmemV + kStagesV * kVStageBytes;
 constexpr int kSmemBytes = kSmemBar + 512 + 1024;
-constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemCols = 512;  // S0 | S1 | S2 | O
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct PairParams {
   int s;            // sequence length
   int bh;           // batch * heads
-  int num_qblocks;  // 512-row query blocks per head
+  int num_qblocks;  // 256-row query blocks per head
   int causal;
   float scale_log2;    // scale * log2(e)
   int64_t row_stride;  // elements between consecutive rows of O (= D)
@@ -70,10 +70,9 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// Number of 128-key blocks the 256 query rows starting at q0 attend to (0 = past the end).
-// Both CTAs of the pair run the same count: their MMAs are one instruction.
+// Number of 128-key blocks the 256 query rows starting at q0 attend to.  Both CTAs of the pair
+// run the same count: their MMAs are one instruction.
 __device__ __forceinline__ int kv_blocks_for_rows(const PairParams& p, int q0) {
-  if (q0 >= p.s) return 0;
   const int all = (p.s + kBlockKV - 1) / kBlockKV;
   if (!p.causal) return all;
   const int last_q = min(q0 + kPairQ, p.s) - 1;
@@ -95,15 +94,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   // q_full, k_full, v_full (both CTAs' TMA loads complete on the leader's copy) and p_full.
   // Waited on locally in each CTA, signalled by the leader's commits: the rest.
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar);
-  uint64_t* q_full = bars;                  // [2]
-  uint64_t* k_full = q_full + 2;            // [kStagesK]
+  uint64_t* q_full = bars;                  // [1]
+  uint64_t* k_full = q_full + 1;            // [kStagesK]
   uint64_t* k_empty = k_full + kStagesK;    // [kStagesK]
   uint64_t* v_full = k_empty + kStagesK;    // [kStagesV]
-  uint64_t* v_empty = v_full + kStagesV;    // [kStagesV]
-  uint64_t* s_full = v_empty + kStagesV;    // [2] S_t written by the tensor core
-  uint64_t* p_full = s_full + 2;            // [2] P_t written (and O_t rescaled) by the softmax warps of both CTAs
-  uint64_t* o_done = p_full + 2;            // [2] O_t += P_t V_j finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+  uint64_t* v_empty = v_full + kStagesV;    // [kStagesV] V stage free = O += P_j V_j finished
+  uint64_t* s_full = v_empty + kStagesV;    // [kBufS] S buffer written by the tensor core
+  uint64_t* p_full = s_full + kBufS;        // [kBufS] P written over the S buffer (and O rescaled) by both CTAs' softmax warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_full + kBufS);
 
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
@@ -120,14 +118,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const int heads_here = min(kHeadGroup, p.bh - group * kHeadGroup);
   const int bh = group * kHeadGroup + in_group % heads_here;
   const int qblk = p.num_qblocks - 1 - in_group / heads_here;
-  const int q_base = qblk * kClusterQ;
-  const int n_kv[2] = {kv_blocks_for_rows(p, q_base), kv_blocks_for_rows(p, q_base + kPairQ)};
-  const int n_max = max(n_kv[0], n_kv[1]);
+  const int q_base = qblk * kPairQ;
+  const int n = kv_blocks_for_rows(p, q_base);
 
   if (warp == 0 && lane == 0) {
     prefetch_tensormap(&tma_q);
     prefetch_tensormap(&tma_k);
     prefetch_tensormap(&tma_v);
+    mbar_init(q_full, 1);
     for (int i = 0; i < kStagesK; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
@@ -136,11 +134,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&q_full[i], 1);
+    for (int i = 0; i < kBufS; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 8);  // 4 softmax warps of tile i in each of the two CTAs
-      mbar_init(&o_done[i], 1);
+      mbar_init(&p_full[i], 8);  // 4 softmax warps in each of the two CTAs
     }
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -154,43 +150,33 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   cluster_sync_all();  // the peer's barriers exist before anything is signalled across CTAs
   tcgen05_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
-  const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128};
-  const uint32_t tmem_o[2] = {tmem_base + 256, tmem_base + 384};
+  const uint32_t tmem_s[kBufS] = {tmem_base, tmem_base + 128, tmem_base + 256};
+  const uint32_t tmem_o = tmem_base + 384;
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs; completions land on the leader's barriers) ----------------
-    if (lane == 0) {
+    if (lane == 0 && n > 0) {
       bool ok = true;
       const int r = static_cast<int>(rank);
-      auto load_q = [&](int t) {
-        if (leader) mbar_expect_tx(&q_full[t], 2 * kQTileBytes);
-        uint8_t* dst = smem + kSmemQ + t * kQTileBytes;
-        const int row0 = q_base + t * kPairQ + r * kTileQ;
-        tma_load_3d_pair(dst, &tma_q, &q_full[t], 0, 0, row0, bh);
-        tma_load_3d_pair(dst + kQPanelBytes, &tma_q, &q_full[t], 0, 64, row0, bh);
-      };
-      auto load_k = [&](int j) {  // this CTA's 64 keys of block j, both head-dim panels
-        const int st = j % kStagesK;
-        if (leader) mbar_expect_tx(&k_full[st], 2 * kKStageBytes);
-        uint8_t* dst = smem + kSmemK + st * kKStageBytes;
-        const int row0 = j * kBlockKV + r * (kBlockKV / 2);
-        tma_load_3d_pair(dst, &tma_k, &k_full[st], 0, 0, row0, bh);
-        tma_load_3d_pair(dst + kKPanelBytes, &tma_k, &k_full[st], 0, 64, row0, bh);
-      };
-      auto load_v = [&](int j) {  // all 128 keys of block j, this CTA's 64 head-dim columns
-        const int st = j % kStagesV;
-        if (leader) mbar_expect_tx(&v_full[st], 2 * kVStageBytes);
-        tma_load_3d_pair(smem + kSmemV + st * kVStageBytes, &tma_v, &v_full[st], 0, r * 64, j * kBlockKV, bh);
-      };
-      if (n_kv[0] > 0) load_q(0);
-      if (n_max > 0) load_k(0);
-      if (n_kv[1] > 0) load_q(1);
-      if (n_max > 0) load_v(0);
-      for (int j = 1; j < n_max && ok; ++j) {
-        if (!mbar_wait<true>(&k_empty[j % kStagesK], ((j / kStagesK) & 1) ^ 1u, status, SILE_ERR_TIMEOUT, 1)) { ok = false; break; }
-        load_k(j);
-        if (!mbar_wait<true>(&v_empty[j % kStagesV], ((j / kStagesV) & 1) ^ 1u, status, SILE_ERR_TIMEOUT, 2)) { ok = false; break; }
-        load_v(j);
+      {
+        if (leader) mbar_expect_tx(q_full, 2 * kQTileBytes);
+        const int row0 = q_base + r * kTileQ;
+        tma_load_3d_pair(smem + kSmemQ, &tma_q, q_full, 0, 0, row0, bh);
+        tma_load_3d_pair(smem + kSmemQ + kQPanelBytes, &tma_q, q_full, 0, 64, row0, bh);
+      }
+      for (int j = 0; j < n && ok; ++j) {
+        const int sk = j % kStagesK, sv = j % kStagesV;
+        // this CTA's 64 keys of block j, both head-dim panels
+        if (!mbar_wait<true>(&k_empty[sk], ((j / kStagesK) & 1) ^ 1u, status, SILE_ERR_TIMEOUT, 1)) { ok = false; break; }
+        if (leader) mbar_expect_tx(&k_full[sk], 2 * kKStageBytes);
+        uint8_t* dk = smem + kSmemK + sk * kKStageBytes;
+        const int krow = j * kBlockKV + r * (kBlockKV / 2);
+        tma_load_3d_pair(dk, &tma_k, &k_full[sk], 0, 0, krow, bh);
+        tma_load_3d_pair(dk + kKPanelBytes, &tma_k, &k_full[sk], 0, 64, krow, bh);
+        // all 128 keys of block j, this CTA's 64 head-dim columns
+        if (!mbar_wait<true>(&v_empty[sv], ((j / kStagesV) & 1) ^ 1u, status, SILE_ERR_TIMEOUT, 2)) { ok = false; break; }
+        if (leader) mbar_expect_tx(&v_full[sv], 2 * kVStageBytes);
+        tma_load_3d_pair(smem + kSmemV + sv * kVStageBytes, &tma_v, &v_full[sv], 0, r * 64, j * kBlockKV, bh);
       }
     }
     __syncwarp();
@@ -198,101 +184,76 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     // ---------------- MMA issuer (leader CTA only) ----------------
     // The whole warp runs this loop and only the tcgen05 instructions are predicated on one
     // elected lane: see umma_ss_f16_if.
-    if (leader && n_max > 0) {
+    if (leader && n > 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(kPairQ, kBlockKV, true, false, false);  // Q K^T: both K-major
+      constexpr uint32_t idesc_o = make_idesc_f16(kPairQ, kD, true, false, true);         // P V: V is MN-major
       const uint32_t el = elect_one() ? 1u : 0u;
+      bool ok = true;
       auto wait = [&](uint64_t* bar, uint32_t parity, int site) {
         const bool w = mbar_wait<true>(bar, parity, status, SILE_ERR_TIMEOUT, site);
         return __all_sync(0xffffffffu, w);
       };
-      constexpr uint32_t idesc_s = make_idesc_f16(kPairQ, kBlockKV, true, false, false);  // Q K^T: both K-major
-      constexpr uint32_t idesc_o = make_idesc_f16(kPairQ, kD, true, false, true);         // P V: V is MN-major
-      bool ok = true;
 
       // Descriptors name offsets that are valid in both CTAs' shared memory; they are built once
       // and inside the unrolled loops only a constant is added to the start-address field.
-      const uint64_t q_desc[2] = {make_smem_desc_sw128(smem_u32(smem + kSmemQ), 16, 1024),
-                                  make_smem_desc_sw128(smem_u32(smem + kSmemQ + kQTileBytes), 16, 1024)};
+      const uint64_t q_desc = make_smem_desc_sw128(smem_u32(smem + kSmemQ), 16, 1024);
       const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(smem + kSmemK), 16, 1024);
       const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(smem + kSmemV), kVStageBytes, 1024);
 
-      auto issue_s = [&](int t, int j) {
-        // S_t (256 x 128 keys) = Q_t (two 64-wide head-dim panels) * K_j^T, 64 keys from each CTA
-        const uint64_t da = q_desc[t], db = k_desc0 + (j % kStagesK) * (kKStageBytes >> 4);
-        const uint32_t d = tmem_s[t];
+      auto issue_s = [&](int j) -> bool {
+        // S_j (256 x 128 keys) = Q (two 64-wide head-dim panels) * K_j^T, 64 keys from each CTA
+        const int sk = j % kStagesK, b = j % kBufS;
+        if (!wait(&k_full[sk], (j / kStagesK) & 1, 3)) return false;
+        tcgen05_fence_after();
+        const uint64_t db = k_desc0 + sk * (kKStageBytes >> 4);
+        const uint32_t d = tmem_s[b];
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk) {
           const uint32_t off_q = (kk >> 2) * (kQPanelBytes >> 4) + (kk & 3) * 2;  // in 16-byte units
           const uint32_t off_k = (kk >> 2) * (kKPanelBytes >> 4) + (kk & 3) * 2;
-          umma_ss_f16_if<2>(el, d, da + off_q, db + off_k, idesc_s, kk != 0 ? 1u : 0u);
+          umma_ss_f16_if<2>(el, d, q_desc + off_q, db + off_k, idesc_s, kk != 0 ? 1u : 0u);
         }
-        commit_both(el, &s_full[t]);
-      };
-      auto issue_pv = [&](int t, int j, bool accumulate, bool last) {
-        // O_t (256 x 128 d) += P_t (TMEM, 8 columns per 16 keys) * V_j (rows = keys, 2048 B per
-        // 16 keys), 64 head-dim columns from each CTA
-        const uint64_t db = v_desc0 + (j % kStagesV) * (kVStageBytes >> 4);
-        const uint32_t d = tmem_o[t], a = tmem_s[t];
-        umma_ts_f16_if<2>(el, d, a, db, idesc_o, accumulate ? 1u : 0u);
-#pragma unroll
-        for (int kk = 1; kk < kBlockKV / 16; ++kk) umma_ts_f16_if<2>(el, d, a + kk * 8, db + kk * 128, idesc_o, 1u);
-        if (last) commit_both(el, &o_done[t]);  // only the epilogue waits for O; see the rescale comment below
+        commit_both(el, &s_full[b]);
+        commit_both(el, &k_empty[sk]);
+        return true;
       };
 
-      // prologue: S_0 for both tiles
-      if (n_kv[0] > 0) ok = ok && wait(&q_full[0], 0, 3);
-      ok = ok && wait(&k_full[0], 0, 4);
-      if (ok) {
+      ok = wait(q_full, 0, 4);
+      for (int j = 0; j < kBufS && j < n && ok; ++j) ok = issue_s(j);
+      for (int j = 0; j < n && ok; ++j) {
+        const int b = j % kBufS, sv = j % kStagesV;
+        if (!wait(&v_full[sv], (j / kStagesV) & 1, 5)) { ok = false; break; }
+        if (!wait(&p_full[b], (j / kBufS) & 1, 6)) { ok = false; break; }
         tcgen05_fence_after();
-        if (n_kv[0] > 0) issue_s(0, 0);
-        if (n_kv[1] > 0) {
-          ok = wait(&q_full[1], 0, 3);
-          if (ok) {
-            tcgen05_fence_after();
-            issue_s(1, 0);
-          }
-        }
-        commit_both(el, &k_empty[0]);
-      }
-      for (int j = 0; j < n_max && ok; ++j) {
-        if (!wait(&v_full[j % kStagesV], (j / kStagesV) & 1, 5)) { ok = false; break; }
-        if (j < n_kv[0]) {
-          if (!wait(&p_full[0], j & 1, 6)) { ok = false; break; }
-          tcgen05_fence_after();
-          issue_pv(0, j, j > 0, j + 1 == n_kv[0]);
-        }
-        if (j + 1 < n_max) {
-          if (!wait(&k_full[(j + 1) % kStagesK], ((j + 1) / kStagesK) & 1, 4)) { ok = false; break; }
-          tcgen05_fence_after();
-        }
-        if (j + 1 < n_kv[0]) issue_s(0, j + 1);
-        if (j < n_kv[1]) {
-          if (!wait(&p_full[1], j & 1, 6)) { ok = false; break; }
-          tcgen05_fence_after();
-          issue_pv(1, j, j > 0, j + 1 == n_kv[1]);
-        }
-        commit_both(el, &v_empty[j % kStagesV]);
-        if (j + 1 < n_kv[1]) issue_s(1, j + 1);
-        if (j + 1 < n_max) commit_both(el, &k_empty[(j + 1) % kStagesK]);
+        // O (256 x 128 d) += P_j (TMEM, 8 columns per 16 keys) * V_j (rows = keys, 2048 B per 16
+        // keys), 64 head-dim columns from each CTA
+        const uint64_t db = v_desc0 + sv * (kVStageBytes >> 4);
+        const uint32_t a = tmem_s[b];
+        umma_ts_f16_if<2>(el, tmem_o, a, db, idesc_o, j > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 1; kk < kBlockKV / 16; ++kk) umma_ts_f16_if<2>(el, tmem_o, a + kk * 8, db + kk * 128, idesc_o, 1u);
+        commit_both(el, &v_empty[sv]);  // also tells the softmax warps that O holds block j
+        if (j + kBufS < n) ok = issue_s(j + kBufS);
       }
     }
     __syncwarp();
-  } else if (warp >= 4) {
-    // ---------------- softmax / correction / epilogue (both CTAs, own rows) ----------------
-    const int t = (warp - 4) >> 2;        // Q tile of this warpgroup
+  } else {
+    // ---------------- softmax / correction / epilogue (both CTAs, own 128 rows) ----------------
     const int quarter = warp & 3;         // TMEM lane quarter of this warp
     const int row_in_tile = quarter * 32 + lane;
-    const int q_tile0 = q_base + t * kPairQ + static_cast<int>(rank) * kTileQ;
+    const int q_tile0 = q_base + static_cast<int>(rank) * kTileQ;
     const int q_idx = q_tile0 + row_in_tile;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t ts = tmem_s[t] + lane_off;
-    const uint32_t to = tmem_o[t] + lane_off;
-    const int n = n_kv[t];
+    const uint32_t to = tmem_o + lane_off;
     float m_used = -INFINITY;  // row max (scaled, log2 domain) that P, l and O currently refer to
     float l = 0.0f;
     bool ok = true;
 
     for (int j = 0; j < n; ++j) {
-      if (!mbar_wait<true>(&s_full[t], j & 1, status, SILE_ERR_TIMEOUT, 7)) ok = false;
+      const int b = j % kBufS;
+      const uint32_t use = (j / kBufS) & 1;  // parity of this use of buffer b
+      const uint32_t ts = tmem_s[b] + lane_off;
+      if (!mbar_wait<true>(&s_full[b], use, status, SILE_ERR_TIMEOUT, 7)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
@@ -335,8 +296,15 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       const float m_sub = (m_used == -INFINITY) ? 0.0f : m_used;
 
       if (j > 0 && __any_sync(0xffffffffu, rescale)) {
-        // O_t already holds block j-1: S_t of block j was issued after P_{j-1} V_{j-1}, MMAs
-        // retire in issue order, and the s_full wait above ordered this thread after all of them.
+        // P_{j-1} V_{j-1} (and with it every earlier one) must have landed in O before it is scaled.
+        // The commit that frees V stage (j-1) % kStagesV says so; these warps only observe that
+        // barrier.  It cannot be a phase ahead (P_j V_j needs the P this step has yet to write)
+        // nor be mistaken for the previous phase (a wait on a parity returns only once the phase
+        // of that parity has completed).
+        if (!mbar_wait<true>(&v_empty[(j - 1) % kStagesV], ((j - 1) / kStagesV) & 1, status, SILE_ERR_TIMEOUT, 8)) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tcgen05_fence_after();
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t orow[32];
@@ -376,11 +344,11 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       tcgen05_wait_st();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(&p_full[t], 0);  // the leader's barrier: 4 warps from each CTA
+      if (lane == 0) mbar_arrive_remote(&p_full[b], 0);  // the leader's barrier: 4 warps from each CTA
     }
 
     if (ok && n > 0) {
-      if (!mbar_wait<true>(&o_done[t], 0, status, SILE_ERR_TIMEOUT, 9)) ok = false;
+      if (!mbar_wait<true>(&v_empty[(n - 1) % kStagesV], ((n - 1) / kStagesV) & 1, status, SILE_ERR_TIMEOUT, 9)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tcgen05_fence_after();
@@ -441,7 +409,7 @@ int attention_pair_launch(const AttnProblem& a, cudaStream_t stream) {
   PairParams p{};
   p.s = static_cast<int>(a.s);
   p.bh = static_cast<int>(a.bh);
-  p.num_qblocks = static_cast<int>((a.s + kClusterQ - 1) / kClusterQ);
+  p.num_qblocks = static_cast<int>((a.s + kPairQ - 1) / kPairQ);
   p.causal = a.causal ? 1 : 0;
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.row_stride = kD;

@@ -7,15 +7,17 @@
 // crates/sile-tile-ir/src/passes/lowering/tile_compute/mma.rs:25-260): online softmax over
 // 128-key blocks with the running row max m, row sum l and an unnormalised accumulator.
 //
-// One CTA = one (batch*head, 256-query block) = two 128-row Q tiles, 12 warps:
+// One CTA = one (batch*head, 256-query block) = two 128-row Q tiles, 10 warps
+// (320 threads leave each softmax thread 200 registers for its 128 scores; 384 would cap it at 168):
 //   warp 0        TMA producer: Q tiles once, then K_j / V_j through 2-stage rings
 //   warp 1        MMA issuer:   S_t = Q_t K_j^T (smem x smem) and O_t += P_t V_j
 //                 (P_t read from TMEM, V_j MN-major from smem), f32 accumulators in TMEM.
 //                 The tiles are served in a fixed order (PV0 S0' PV1 S1' ...), which keeps their
 //                 softmax phases apart; one issuing warp per tile was measured ~17 % slower
 //                 because the tiles then fall into step and their softmaxes collide.
-//   warps 4..7    softmax of Q tile 0 (thread r owns row r = TMEM lane r)
-//   warps 8..11   softmax of Q tile 1
+//   warps 2..5    softmax of Q tile 0 (thread r owns row r = TMEM lane r; a warp reaches the TMEM
+//                 lane quarter warp % 4, and any four consecutive warps cover all four)
+//   warps 6..9    softmax of Q tile 1
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 columns each; P_t (bf16 pairs) overwrites the
 // first 64 columns of S_t.  Per tile the chain is S -> softmax -> PV -> next S; the softmax of one
 // tile runs under the MMAs of the other.  O is rescaled only when the row max has grown by more
@@ -42,7 +44,7 @@ constexpr int kBlockKV = 128;
 constexpr int kPanelBytes = 128 * 64 * 2;   // one [128 rows x 64 cols] 128B-swizzled panel
 constexpr int kTileBytes = 2 * kPanelBytes;  // [128 x 128] bf16
 constexpr int kStagesKV = 2;
-constexpr int kThreads = 384;
+constexpr int kThreads = 320;
 constexpr int kSmemQ = 0;
 constexpr int kSmemK = kSmemQ + 2 * kTileBytes;
 constexpr int kSmemV = kSmemK + kStagesKV * kTileBytes;
@@ -252,9 +254,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       }
     }
     __syncwarp();
-  } else if (warp >= 4) {
+  } else if (warp >= 2) {
     // ---------------- softmax / correction / epilogue ----------------
-    const int t = (warp - 4) >> 2;        // Q tile of this warpgroup
+    const int t = (warp - 2) >> 2;        // Q tile of this group of four warps
     const int quarter = warp & 3;         // TMEM lane quarter of this warp
     const int row_in_tile = quarter * 32 + lane;
     const int q_idx = q_base + t * kTileQ + row_in_tile;
@@ -406,9 +408,11 @@ int attention_launch(const AttnProblem& a, cudaStream_t stream) {
     if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(SILE_ERR_UNSUPPORTED, "attention: buffers must be 16-byte aligned");
   if (!(a.scale > 0.0f)) return fail(SILE_ERR_INVALID, "attention: scale must be positive");
 
-  // SILE_CUDA_ATTN_KERNEL=pair selects the CTA-pair kernel (attn_pair_sm100.cu): half the K / V
-  // traffic per SM and a deeper ring, but twice the tcgen05.commit instructions and cross-CTA
-  // hand-offs; measured ~12 % slower than this file's kernel, which stays the default.
+  // SILE_CUDA_ATTN_KERNEL=pair selects the CTA-pair kernel (attn_pair_sm100.cu): one Q tile per
+  // SM, K / V shared by the pair, three S buffers so the softmax never waits for the tensor core.
+  // Its single softmax warp per scheduler is latency-bound (~1500 cycles per 128 keys against
+  // ~1200 when two warps share the MUFU pipe), which leaves it ~18 % behind this file's kernel;
+  // that one stays the default.
   const char* which = std::getenv("SILE_CUDA_ATTN_KERNEL");
   if (which && std::strcmp(which, "pair") == 0) return attention_pair_launch(a, stream);
 
