@@ -124,6 +124,50 @@ __global__ void softmax_rows_kernel(const float* __restrict__ x, int64_t ldx, fl
   }
 }
 
+// Rows of up to 128 * kChunks columns with 16-byte aligned rows: each lane holds kChunks float4
+// (the row is read once, 512 bytes per warp load), all loads of a row are issued before the first
+// use, exp is ex2.approx on (x - max) * log2(e) and the division becomes one reciprocal per row.
+template <int kChunks>
+__global__ void softmax_rows_vec4_kernel(const float* __restrict__ x, int64_t ldx, float* __restrict__ y, int64_t ldy, int64_t rows,
+                                         int cols4) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int64_t warp_global = blockIdx.x * static_cast<int64_t>(warps_per_block) + (threadIdx.x >> 5);
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps_per_block;
+  constexpr float kLog2e = 1.4426950408889634f;
+  for (int64_t row = warp_global; row < rows; row += nwarps) {
+    const float4* xr = reinterpret_cast<const float4*>(x + row * ldx);
+    float4* yr = reinterpret_cast<float4*>(y + row * ldy);
+    float4 v[kChunks];
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i) {
+      const int c = lane + 32 * i;
+      v[i] = c < cols4 ? __ldcs(xr + c) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    }
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i) mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    mx = warp_max(mx);
+    const float off = mx * kLog2e;
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i) {
+      v[i].x = exp2f(fmaf(v[i].x, kLog2e, -off));
+      v[i].y = exp2f(fmaf(v[i].y, kLog2e, -off));
+      v[i].z = exp2f(fmaf(v[i].z, kLog2e, -off));
+      v[i].w = exp2f(fmaf(v[i].w, kLog2e, -off));
+      sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i) {
+      const int c = lane + 32 * i;
+      if (c < cols4) __stcs(yr + c, make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv));
+    }
+  }
+}
+
 // out[0] += sum(a[0..n))   (examples/parallel_reduce.rs:3-9: per-tile reduce_sum then
 // atomic_add; block_scalar.rs:98-157).  One red.global.add.f32 per block; the order of
 // the atomics is nondeterministic here as it is under OpenMP in the reference.
@@ -190,6 +234,47 @@ __global__ void matvec_kernel(const float* __restrict__ x, const float* __restri
   }
 }
 
+// K <= 128 * kChunks, 16-byte aligned: the lane's share of y stays in registers for every row the
+// warp handles, and two rows are in flight per step (all their loads issued before the first FMA).
+template <int kChunks>
+__global__ void matvec_vec4_kernel(const float* __restrict__ x, const float* __restrict__ y, float* __restrict__ z, int64_t m, int k4) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int64_t warp_global = blockIdx.x * static_cast<int64_t>(warps_per_block) + (threadIdx.x >> 5);
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps_per_block;
+  const float4* y4 = reinterpret_cast<const float4*>(y);
+  float4 yv[kChunks];
+#pragma unroll
+  for (int i = 0; i < kChunks; ++i) {
+    const int c = lane + 32 * i;
+    yv[i] = c < k4 ? __ldg(y4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int64_t row = 2 * warp_global; row < m; row += 2 * nwarps) {
+    const float4* x0 = reinterpret_cast<const float4*>(x) + row * k4;
+    const bool two = row + 1 < m;
+    const float4* x1 = x0 + (two ? k4 : 0);
+    float4 a[kChunks], b[kChunks];
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i) {
+      const int c = lane + 32 * i;
+      a[i] = c < k4 ? __ldcs(x0 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+      b[i] = c < k4 ? __ldcs(x1 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i) {
+      acc0 += a[i].x * yv[i].x + a[i].y * yv[i].y + a[i].z * yv[i].z + a[i].w * yv[i].w;
+      acc1 += b[i].x * yv[i].x + b[i].y * yv[i].y + b[i].z * yv[i].z + b[i].w * yv[i].w;
+    }
+    acc0 = warp_sum(acc0);
+    acc1 = warp_sum(acc1);
+    if (lane == 0) {
+      z[row] = acc0;
+      if (two) z[row + 1] = acc1;
+    }
+  }
+}
+
 // dst[r][j*cols + c] = src[j][r][c], 16 bytes per thread per step.
 __global__ void unshard_columns_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int parts, int64_t rows, int cols16) {
   const int64_t per_part = rows * cols16;
@@ -239,7 +324,17 @@ int relu_launch(float* x, int64_t n, cudaStream_t stream) {
 int softmax_rows_launch(const float* x, int64_t ldx, float* y, int64_t ldy, int64_t rows, int64_t cols, cudaStream_t stream) {
   if (rows <= 0) return SILE_OK;
   if (cols > (1ll << 30)) return fail(SILE_ERR_INVALID, "softmax: row too long");
-  softmax_rows_kernel<<<grid_for(rows * 32, 8), kThreads, 0, stream>>>(x, ldx, y, ldy, rows, static_cast<int>(cols));
+  const bool vec = cols % 4 == 0 && cols <= 1024 && ldx % 4 == 0 && ldy % 4 == 0 && aligned16(x) && aligned16(y);
+  if (vec) {
+    const int cols4 = static_cast<int>(cols / 4);
+    const int grid = grid_for(rows * 32, 8);
+    if (cols4 <= 32) softmax_rows_vec4_kernel<1><<<grid, kThreads, 0, stream>>>(x, ldx, y, ldy, rows, cols4);
+    else if (cols4 <= 64) softmax_rows_vec4_kernel<2><<<grid, kThreads, 0, stream>>>(x, ldx, y, ldy, rows, cols4);
+    else if (cols4 <= 128) softmax_rows_vec4_kernel<4><<<grid, kThreads, 0, stream>>>(x, ldx, y, ldy, rows, cols4);
+    else softmax_rows_vec4_kernel<8><<<grid, kThreads, 0, stream>>>(x, ldx, y, ldy, rows, cols4);
+  } else {
+    softmax_rows_kernel<<<grid_for(rows * 32, 8), kThreads, 0, stream>>>(x, ldx, y, ldy, rows, static_cast<int>(cols));
+  }
   SILE_CUDA_TRY(cudaGetLastError());
   return SILE_OK;
 }
@@ -254,7 +349,16 @@ int reduce_sum_launch(const float* a, int64_t n, float* out, cudaStream_t stream
 int matvec_launch(const float* x, const float* y, float* z, int64_t m, int64_t k, cudaStream_t stream) {
   if (m <= 0) return SILE_OK;
   const int vec = aligned16(x) && aligned16(y) && (k % 4 == 0);
-  matvec_kernel<<<grid_for(m * 32, 8), kThreads, 0, stream>>>(x, y, z, m, k, vec);
+  if (vec && k <= 1024) {
+    const int k4 = static_cast<int>(k / 4);
+    const int grid = grid_for((m + 1) / 2 * 32, 8);
+    if (k4 <= 32) matvec_vec4_kernel<1><<<grid, kThreads, 0, stream>>>(x, y, z, m, k4);
+    else if (k4 <= 64) matvec_vec4_kernel<2><<<grid, kThreads, 0, stream>>>(x, y, z, m, k4);
+    else if (k4 <= 128) matvec_vec4_kernel<4><<<grid, kThreads, 0, stream>>>(x, y, z, m, k4);
+    else matvec_vec4_kernel<8><<<grid, kThreads, 0, stream>>>(x, y, z, m, k4);
+  } else {
+    matvec_kernel<<<grid_for(m * 32, 8), kThreads, 0, stream>>>(x, y, z, m, k, vec);
+  }
   SILE_CUDA_TRY(cudaGetLastError());
   return SILE_OK;
 }

@@ -63,7 +63,9 @@ def test_softmax_golden(sb):
     assert np.abs(y.sum(axis=1) - 1.0).max() < 1e-4
 
 
-@pytest.mark.parametrize("rows,cols", [(64, 8), (333, 1000), (16, 4096)])
+# vector path (cols % 4 == 0, <= 1024; 1, 2, 4 and 8 float4 per lane, ragged last chunk), scalar
+# register-cached path (odd cols), and the long-row path (> 1024)
+@pytest.mark.parametrize("rows,cols", [(64, 8), (65, 36), (50, 128), (37, 260), (333, 1000), (129, 1024), (40, 1023), (16, 4096)])
 def test_softmax_matches_oracle(sb, oracle, rows, cols):
     x = uniform((rows, cols), 7) * 8
     y = np.zeros_like(x)
@@ -112,3 +114,17 @@ def test_mlp_chain(sb, oracle):
     sb.kernel_call("relu", [out1])
     want = np.maximum((x.astype(np.float64) @ w0) @ w1, 0)
     assert np.abs(out1 - want).max() < 1e-3 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("m,k", [(64, 8), (33, 36), (257, 200), (1001, 1024), (64, 1032), (50, 77)])
+def test_matvec_matches_oracle(sb, oracle, m, k):
+    """Register-cached vector path (k % 4 == 0, k <= 1024; odd and even row counts), the long-row
+    vector path and the scalar path."""
+    x, y = uniform((m, k), 11), uniform(k, 12)
+    z = np.zeros(m, np.float32)
+    want = np.zeros(m, np.float32)
+    sb.bind_consts("matvec", (1, 1))
+    sb.kernel_call("matvec", [x, y, z], grid=(m, 1, 1))
+    oracle.lib.sile_oracle_bind_matvec(1, 1)
+    oracle.launch("matvec", [x, y, want], grid=(m, 1, 1))
+    assert np.abs(z - want).max() < 1e-3 * max(np.abs(want).max(), 1e-6)
