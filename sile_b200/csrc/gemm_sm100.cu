@@ -295,7 +295,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 // (cluster rank 0) issues tcgen05.mma.cta_group::2 with M = 256, N = 256 and each CTA's TMEM
 // receives its 128 accumulator rows.  Every TMA load completes on the LEADER's full barrier;
 // the leader's commits release the stage, and publish the accumulator, in both CTAs; both
-// CTAs' epilogue warps report to the leader's tmem_empty barrier.  No load is multicast.
+// CTAs' epilogue warps report to the leader's tmem_empty barrier.  Every load is a plain per-CTA TMA load.
 constexpr int kPairStages = 6;
 constexpr int kPairABytes = 128 * kBK * 2;
 constexpr int kPairBBytes = 128 * kBK * 2;
