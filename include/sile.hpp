@@ -22,13 +22,22 @@
 // devices can be constructed, as in the reference, and fail at apply() with UnsupportedBackend,
 // exactly as the reference's Cuda device does today, kernel_launcher.rs:69-71); Result<T> becomes
 // a thrown sile::Error.
+//
+// Beyond the reference: a Tensor made for a Cuda device LIVES on that device (the reference's is
+// a host Vec<f32> that every GPU backend uploads per launch, tensor.rs:5-9,
+// metal/mod.rs:117-125) and a Cuda Stream is a real stream.  from_vec / zeros / ones / random
+// upload once, apply() launches asynchronously on the stream with device pointers
+// (sile_cuda_launch), and to_vec(stream) synchronises the stream and downloads.  A chain such as
+// gemm -> matvec -> relu (examples/mlp.rs) therefore moves no data between its kernels.
 #ifndef SILE_HPP
 #define SILE_HPP
 
+#include <algorithm>
 #include <array>
 #include <cstdint>
 #include <cstdlib>
 #include <initializer_list>
+#include <memory>
 #include <random>
 #include <stdexcept>
 #include <string>
@@ -91,36 +100,47 @@ class Device {
   int index_;
 };
 
-// crates/sile-core/src/stream.rs:4-19.  synchronize() is a no-op in the reference; every
-// launch below is complete on return, so it only surfaces a recorded device-side time-out.
+// crates/sile-core/src/stream.rs:4-19.  synchronize() is a no-op in the reference; here a Cuda
+// stream is a real one: launches are queued on it and synchronize() waits for them and reports a
+// device-side time-out recorded meanwhile.
 class Stream {
  public:
   const Device& device() const { return device_; }
+  void* handle() const { return handle_.get(); }  // cudaStream_t for a Cuda device, else null
   void synchronize() const {
     if (device_.kind() != Device::Kind::Cuda) return;
-    const int rc = sile_cuda_synchronize(nullptr);
+    const int rc = sile_cuda_synchronize(handle());
     if (rc != SILE_OK) throw Error(Error::Kind::Io, sile_cuda_last_error());
   }
 
  private:
   friend class Device;
-  explicit Stream(Device d) : device_(std::move(d)) {}
+  explicit Stream(Device d) : device_(std::move(d)) {
+    if (device_.kind() != Device::Kind::Cuda) return;
+    if (sile_cuda_set_device(device_.index()) != SILE_OK) throw Error(Error::Kind::InvalidDevice, sile_cuda_last_error());
+    void* st = nullptr;
+    if (sile_cuda_stream_create(&st) != SILE_OK) throw Error(Error::Kind::Io, sile_cuda_last_error());
+    handle_ = std::shared_ptr<void>(st, [](void* p) { sile_cuda_stream_destroy(p); });
+  }
   Device device_;
+  std::shared_ptr<void> handle_;
 };
 inline Stream Device::create_stream() const { return Stream(*this); }
 
-// crates/sile/src/tensor.rs:5-88: a host Vec<f32> with a shape and the device it was made for.
+// crates/sile/src/tensor.rs:5-88: f32 data with a shape and the device it was made for.  On a Cuda
+// device the data is a device buffer (shared by copies of the Tensor, freed with the last one);
+// on the other devices it is the reference's host vector.
 class Tensor {
  public:
   using Shape = std::vector<int64_t>;
   static Tensor zeros(Shape shape, const Device& d) { return filled(std::move(shape), 0.0f, d); }
   static Tensor ones(Shape shape, const Device& d) { return filled(std::move(shape), 1.0f, d); }
   static Tensor random(Shape shape, const Device& d) {  // uniform [0, 1), unseeded, as tensor.rs:39-50
-    Tensor t = filled(std::move(shape), 0.0f, d);
+    std::vector<float> host(count(shape));
     std::mt19937 rng(std::random_device{}());
     std::uniform_real_distribution<float> u(0.0f, 1.0f);
-    for (float& x : t.data_) x = u(rng);
-    return t;
+    for (float& x : host) x = u(rng);
+    return Tensor(std::move(host), std::move(shape), d);
   }
   static Tensor from_vec(std::vector<float> data, Shape shape, const Device& d) {
     const size_t len = count(shape);
@@ -129,14 +149,35 @@ class Tensor {
     return Tensor(std::move(data), std::move(shape), d);
   }
   const Shape& shape() const { return shape_; }
-  size_t len() const { return data_.size(); }
-  const float* as_ptr() const { return data_.data(); }
-  float* as_mut_ptr() { return data_.data(); }
-  std::vector<float> to_vec(const Stream&) const { return data_; }
+  size_t len() const { return len_; }
+  // The pointer a kernel argument carries (tensor.rs:64-81): device memory on a Cuda device.
+  const float* as_ptr() const { return dev_ ? static_cast<const float*>(dev_.get()) : host_.data(); }
+  float* as_mut_ptr() { return dev_ ? static_cast<float*>(dev_.get()) : host_.data(); }
+  // tensor.rs:83-85.  On a Cuda device: waits for the work queued on `stream`, then downloads.
+  std::vector<float> to_vec(const Stream& stream) const {
+    if (!dev_) return host_;
+    std::vector<float> out(len_);
+    const void* st = stream.device() == device_ ? stream.handle() : nullptr;
+    if (sile_cuda_set_device(device_.index()) != SILE_OK) throw Error(Error::Kind::InvalidDevice, sile_cuda_last_error());
+    if (sile_cuda_memcpy_d2h(out.data(), dev_.get(), len_ * sizeof(float), const_cast<void*>(st)) != SILE_OK)
+      throw Error(Error::Kind::Io, sile_cuda_last_error());
+    return out;
+  }
   const Device& device() const { return device_; }
+  bool on_device() const { return static_cast<bool>(dev_); }
 
  private:
-  Tensor(std::vector<float> data, Shape shape, Device d) : data_(std::move(data)), shape_(std::move(shape)), device_(std::move(d)) {}
+  Tensor(std::vector<float> data, Shape shape, Device d) : shape_(std::move(shape)), device_(std::move(d)), len_(data.size()) {
+    if (device_.kind() != Device::Kind::Cuda) {
+      host_ = std::move(data);
+      return;
+    }
+    if (sile_cuda_set_device(device_.index()) != SILE_OK) throw Error(Error::Kind::InvalidDevice, sile_cuda_last_error());
+    void* p = nullptr;
+    if (sile_cuda_malloc(&p, std::max<size_t>(len_, 1) * sizeof(float)) != SILE_OK) throw Error(Error::Kind::Io, sile_cuda_last_error());
+    dev_ = std::shared_ptr<void>(p, [](void* q) { sile_cuda_free(q); });
+    if (sile_cuda_memcpy_h2d(p, data.data(), len_ * sizeof(float), nullptr) != SILE_OK) throw Error(Error::Kind::Io, sile_cuda_last_error());
+  }
   static size_t count(const Shape& s) {
     size_t n = 1;
     for (int64_t v : s) n *= static_cast<size_t>(v);
@@ -146,9 +187,11 @@ class Tensor {
     const size_t n = count(shape);
     return Tensor(std::vector<float>(n, v), std::move(shape), d);
   }
-  std::vector<float> data_;
+  std::vector<float> host_;
+  std::shared_ptr<void> dev_;
   Shape shape_;
   Device device_;
+  size_t len_ = 0;
 };
 
 // crates/sile-core/src/kernel.rs:4-14
@@ -182,7 +225,9 @@ class KernelLauncher {
       buffers.push_back(a.mut_ptr);
       shapes.insert(shapes.end(), a.shape->begin(), a.shape->end());
     }
-    rc = sile_cuda_launch_host(&desc_, buffers.data(), shapes.data(), static_cast<int64_t>(shapes.size()), launch_.grid.data());
+    // Arguments are device buffers of tensors made for a Cuda device; the launch is queued on the
+    // stream and errors of the kernel itself surface at Stream::synchronize / Tensor::to_vec.
+    rc = sile_cuda_launch(&desc_, buffers.data(), shapes.data(), static_cast<int64_t>(shapes.size()), launch_.grid.data(), stream.handle());
     if (rc == SILE_OK) return;
     const std::string msg = sile_cuda_last_error();
     switch (rc) {

@@ -194,6 +194,21 @@ int sile_cuda_device_count(void);
  * the last call (SILE_ERR_TIMEOUT) and clears it. */
 int sile_cuda_synchronize(void* stream);
 
+/* Device-resident tensors and real streams.  The reference's Tensor is a host Vec<f32> and every
+ * GPU backend re-uploads it per launch (crates/sile/src/tensor.rs:5-9;
+ * crates/sile-backend/src/metal/mod.rs:117-125); with these a binding keeps tensors on the device,
+ * launches through sile_cuda_launch on a stream and copies only at Tensor::from_vec / to_vec.
+ * No counterpart in the reference.  Buffers are cudaMalloc allocations (256-byte aligned) of the
+ * current device; copies are ordered on `stream` and complete on return (the host side is pageable
+ * memory); sile_cuda_memcpy_d2h also reports a device-side time-out like sile_cuda_synchronize. */
+int sile_cuda_malloc(void** dev_ptr, size_t bytes);
+int sile_cuda_free(void* dev_ptr);
+int sile_cuda_memcpy_h2d(void* dev_dst, const void* host_src, size_t bytes, void* stream);
+int sile_cuda_memcpy_d2h(void* host_dst, const void* dev_src, size_t bytes, void* stream);
+int sile_cuda_memset(void* dev_dst, int byte_value, size_t bytes, void* stream);
+int sile_cuda_stream_create(void** stream);
+int sile_cuda_stream_destroy(void* stream);
+
 /* Scratch the f32 matmul needs on the device for a given problem, in bytes
  * (0 for 16-bit inputs).  sile_cuda_launch obtains it from the stream-ordered
  * allocator itself; the figure is exposed for capacity planning. */

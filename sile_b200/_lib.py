@@ -19,7 +19,9 @@ EXPORTED_SYMBOLS = (
     "sile_kernel_parallel_reduce", "sile_kernel_matvec", "sile_cuda_bind_consts",
     "sile_cuda_launch", "sile_cuda_launch_host", "sile_cuda_matmul_shard",
     "sile_cuda_matmul_allgather", "sile_cuda_unshard_columns", "sile_cuda_matmul_f32_noalloc", "sile_cuda_set_device",
-    "sile_cuda_device_count", "sile_cuda_synchronize", "sile_cuda_matmul_workspace_bytes",
+    "sile_cuda_device_count", "sile_cuda_synchronize", "sile_cuda_malloc", "sile_cuda_free",
+    "sile_cuda_memcpy_h2d", "sile_cuda_memcpy_d2h", "sile_cuda_memset", "sile_cuda_stream_create",
+    "sile_cuda_stream_destroy", "sile_cuda_matmul_workspace_bytes",
     "sile_cuda_last_error", "sile_cuda_last_status", "sile_cuda_version",
 )
 
@@ -65,6 +67,13 @@ def lib() -> C.CDLL:
     L.sile_cuda_matmul_f32_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [_i64] * 6 + [C.c_void_p, C.c_int32]
     L.sile_cuda_set_device.argtypes = [C.c_int]
     L.sile_cuda_synchronize.argtypes = [C.c_void_p]
+    L.sile_cuda_malloc.argtypes = [C.POINTER(C.c_void_p), C.c_size_t]
+    L.sile_cuda_free.argtypes = [C.c_void_p]
+    L.sile_cuda_memcpy_h2d.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    L.sile_cuda_memcpy_d2h.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    L.sile_cuda_memset.argtypes = [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]
+    L.sile_cuda_stream_create.argtypes = [C.POINTER(C.c_void_p)]
+    L.sile_cuda_stream_destroy.argtypes = [C.c_void_p]
     L.sile_cuda_matmul_workspace_bytes.argtypes = [_i64, _i64, _i64, C.c_int32]
     L.sile_cuda_matmul_workspace_bytes.restype = C.c_size_t
     L.sile_cuda_last_error.restype = C.c_char_p

@@ -493,6 +493,62 @@ int sile_cuda_synchronize(void* stream) {
   return read_and_clear_status();
 }
 
+int sile_cuda_malloc(void** dev_ptr, size_t bytes) {
+  if (!dev_ptr) return fail(SILE_ERR_INVALID, "null argument");
+  *dev_ptr = nullptr;
+  if (int rc = check_device()) return rc;
+  if (bytes == 0) return SILE_OK;
+  SILE_CUDA_TRY(cudaMalloc(dev_ptr, bytes));
+  return SILE_OK;
+}
+
+int sile_cuda_free(void* dev_ptr) {
+  if (!dev_ptr) return SILE_OK;
+  SILE_CUDA_TRY(cudaFree(dev_ptr));
+  return SILE_OK;
+}
+
+int sile_cuda_memcpy_h2d(void* dev_dst, const void* host_src, size_t bytes, void* stream) {
+  if (bytes == 0) return SILE_OK;
+  if (!dev_dst || !host_src) return fail(SILE_ERR_INVALID, "null argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SILE_CUDA_TRY(cudaMemcpyAsync(dev_dst, host_src, bytes, cudaMemcpyHostToDevice, st));
+  SILE_CUDA_TRY(cudaStreamSynchronize(st));
+  return SILE_OK;
+}
+
+int sile_cuda_memcpy_d2h(void* host_dst, const void* dev_src, size_t bytes, void* stream) {
+  if (bytes == 0) return SILE_OK;
+  if (!host_dst || !dev_src) return fail(SILE_ERR_INVALID, "null argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SILE_CUDA_TRY(cudaMemcpyAsync(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost, st));
+  SILE_CUDA_TRY(cudaStreamSynchronize(st));
+  return read_and_clear_status();
+}
+
+int sile_cuda_memset(void* dev_dst, int byte_value, size_t bytes, void* stream) {
+  if (bytes == 0) return SILE_OK;
+  if (!dev_dst) return fail(SILE_ERR_INVALID, "null argument");
+  SILE_CUDA_TRY(cudaMemsetAsync(dev_dst, byte_value, bytes, static_cast<cudaStream_t>(stream)));
+  return SILE_OK;
+}
+
+int sile_cuda_stream_create(void** stream) {
+  if (!stream) return fail(SILE_ERR_INVALID, "null argument");
+  *stream = nullptr;
+  if (int rc = check_device()) return rc;
+  cudaStream_t st = nullptr;
+  SILE_CUDA_TRY(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+  *stream = st;
+  return SILE_OK;
+}
+
+int sile_cuda_stream_destroy(void* stream) {
+  if (!stream) return SILE_OK;
+  SILE_CUDA_TRY(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
+  return SILE_OK;
+}
+
 size_t sile_cuda_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int32_t in_dtype) {
   GemmProblem p;
   p.m = m; p.n = n; p.k = k; p.in_dtype = in_dtype;
