@@ -479,25 +479,59 @@ def main():
         o_full = torch.empty(bh_total, s_len, 128, device=dev, dtype=torch.bfloat16)
         akl = sb.attention(q, k, v, o_slab, 1.0 / 128 ** 0.5, True)
 
-        def attn_step():
+        def attn_step_nccl():
             akl.apply()
             dist.all_gather_into_tensor(o_full, o_slab)
 
-        for _ in range(3):
-            attn_step()
-        barrier()
-        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a0.record()
-        for _ in range(10):
-            attn_step()
-        a1.record()
-        barrier()
-        ams = max_over_ranks(a0.elapsed_time(a1)) / 10
+        def time_attn(fn):
+            for _ in range(3):
+                fn()
+            barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(10):
+                fn()
+            a1.record()
+            barrier()
+            return max_over_ranks(a0.elapsed_time(a1)) / 10
+
         afl = 4.0 * bh_total * s_len * s_len * 128 * 0.5
+        nccl_ms = time_attn(attn_step_nccl)
+        fused_ms = None
+        if args.exchange in ("auto", "fused"):
+            try:
+                # O lives in symmetric memory; every CTA's epilogue TMA-stores its rows into every
+                # rank's buffer, so the exchange runs under the remaining CTAs' compute.
+                import torch.distributed._symmetric_memory as symm_mem
+                o_sym = symm_mem.empty((bh_total, s_len, 128), dtype=torch.bfloat16, device=dev)
+                ohdl = symm_mem.rendezvous(o_sym, dist.group.WORLD)
+                optrs = [int(x) for x in ohdl.buffer_ptrs]
+                o_sym.zero_()
+
+                def attn_step_fused():
+                    sb.attention_allgather(q, k, v, optrs, rank, 1.0 / 128 ** 0.5, True)
+                    ohdl.barrier(channel=1, timeout_ms=20000)
+
+                fused_ms = time_attn(attn_step_fused)
+                torch.cuda.synchronize()
+                barrier()
+                fused_matches = bool(torch.equal(o_sym, o_full))
+                del o_sym
+            except Exception as e:
+                if args.exchange == "fused":
+                    raise
+                if rank == 0:
+                    print(f"fused attention all-gather unavailable ({e!r})", file=sys.stderr)
+        ams = fused_ms if fused_ms is not None else nccl_ms
         atf = afl / (ams * 1e-3) / 1e12
         extras["attn_fwd_b8_h32_s8192_d128_causal_sharded"] = {
             "ms": ams, "tflops_whole_job": atf, "per_gpu_tflops": atf / p,
-            "exchange": "NCCL all-gather of the output slabs (rank-major = final [B*H, S, D] layout)"}
+            "exchange": ("all-gather folded into the kernel: every CTA TMA-stores its rows of O into every rank's buffer "
+                         "(symmetric memory), one device barrier per step" if fused_ms is not None else
+                         "NCCL all-gather of the output slabs (rank-major = final [B*H, S, D] layout)"),
+            "nccl_all_gather_ms": nccl_ms, "nccl_all_gather_tflops_whole_job": afl / (nccl_ms * 1e-3) / 1e12}
+        if fused_ms is not None:
+            extras["attn_fwd_b8_h32_s8192_d128_causal_sharded"]["fused_matches_nccl_result"] = fused_matches
         sb.synchronize()
         del q, k, v, o_slab, o_full
 

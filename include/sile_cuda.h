@@ -145,6 +145,19 @@ int sile_cuda_matmul_allgather(const SileKernelDesc* desc, const void* a, const 
                                void* const* c_peers, int32_t world, int32_t rank, int64_t m,
                                int64_t n_total, int64_t k, void* stream);
 
+/* Attention forward over this rank's slab of heads with the all-gather of O folded into the
+ * kernel's epilogue: rank `rank` of `world` (<= 8) holds q, k, v for heads
+ * [rank * bh_local, (rank + 1) * bh_local) as [bh_local, S, 128] bf16 and every CTA stores its
+ * rows of O (TMA stores, full 128-byte lines) into the [world * bh_local, S, 128] buffer of
+ * EVERY rank.  o_peers[i] is the base of rank i's buffer as mapped into this process
+ * (o_peers[rank] is the local one).  The kernel waits on no other GPU; when the call has
+ * completed on every rank and the ranks have synchronised, each holds the whole O in its final
+ * layout.  desc: op SILE_OP_ATTENTION, bf16 in and out, `scale`, `causal`.  The reference shards
+ * nothing; this follows the batch x head split with one all-gather of the outputs. */
+int sile_cuda_attention_allgather(const SileKernelDesc* desc, const void* q, const void* k,
+                                  const void* v, void* const* o_peers, int32_t world, int32_t rank,
+                                  int64_t bh_local, int64_t s, void* stream);
+
 /* Lays the rank-major result of an all-gather of packed column blocks,
  * src[parts][rows][cols], out as one row-major matrix dst[rows][parts*cols].
  * `dtype` is a SILE_DTYPE_* giving the element size. */

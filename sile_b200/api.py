@@ -185,6 +185,19 @@ def unshard_columns(dst, src, stream=None) -> None:
                                                 _dtype_code(src), _stream_handle(stream)))
 
 
+def attention_allgather(q, k, v, o_ptrs, rank: int, scale: float, causal: bool = False, stream=None) -> None:
+    """Attention forward over this rank's heads whose epilogue stores O into every rank's buffer.
+
+    ``q, k, v`` are this rank's [bh_local, S, 128] bf16 slabs; ``o_ptrs`` lists the device address
+    of each rank's [world * bh_local, S, 128] bf16 buffer as mapped into this process
+    (``o_ptrs[rank]`` is the local one)."""
+    desc = make_desc(OP_ATTENTION, _dtype_code(q), DTYPE_BF16, causal=causal, scale=scale)
+    bh_local = q.numel() // (q.shape[-1] * q.shape[-2])
+    arr = (C.c_void_p * len(o_ptrs))(*[int(p) for p in o_ptrs])
+    _check(_lib.lib().sile_cuda_attention_allgather(C.byref(desc), q.data_ptr(), k.data_ptr(), v.data_ptr(), arr, len(o_ptrs), rank,
+                                                    bh_local, q.shape[-2], _stream_handle(stream)))
+
+
 def matmul_allgather(a, b_shard, c_ptrs, rank: int, n_total: int, out_dtype, bm=1, bn=1, bk=1, stream=None) -> None:
     """Column-block matmul whose epilogue stores the block into every rank's full C.
 

@@ -642,6 +642,31 @@ int sile_cuda_matmul_allgather(const SileKernelDesc* desc, const void* a, const 
   return rc;
 }
 
+int sile_cuda_attention_allgather(const SileKernelDesc* desc, const void* q, const void* k, const void* v, void* const* o_peers,
+                                  int32_t world, int32_t rank, int64_t bh_local, int64_t s, void* stream) {
+  if (int rc = validate_desc(desc)) return rc;
+  if (int rc = check_device()) return rc;
+  if (desc->op != SILE_OP_ATTENTION) return fail(SILE_ERR_INVALID, "attention_allgather: description is not an attention");
+  if (desc->in_dtype != SILE_DTYPE_BF16 || desc->out_dtype != SILE_DTYPE_BF16)
+    return fail(SILE_ERR_UNSUPPORTED, "attention: bf16 in / bf16 out only");
+  if (!o_peers) return fail(SILE_ERR_INVALID, "null buffer");
+  if (world < 1 || world > 8 || rank < 0 || rank >= world)
+    return fail(SILE_ERR_INVALID, "attention_allgather: bad rank %d of %d (at most 8)", rank, world);
+  AttnProblem p;
+  p.q = q; p.k = k; p.v = v;
+  p.bh = bh_local; p.s = s; p.d = 128;
+  p.scale = desc->scale;
+  p.causal = desc->causal;
+  p.num_peers = world;
+  p.peer_first = rank;
+  p.bh_total = bh_local * world;
+  p.bh_offset = bh_local * rank;
+  for (int i = 0; i < world; ++i) p.peer_o[i] = o_peers[i];
+  const int rc = attention_launch(p, static_cast<cudaStream_t>(stream));
+  if (rc == SILE_OK) t_last_status = SILE_OK;
+  return rc;
+}
+
 int sile_cuda_unshard_columns(void* dst, const void* src, int64_t parts, int64_t rows, int64_t cols, int32_t dtype, void* stream) {
   if (int rc = check_device()) return rc;
   const int rc = unshard_columns_launch(dst, src, parts, rows, cols, static_cast<int>(dtype_size(dtype)), static_cast<cudaStream_t>(stream));

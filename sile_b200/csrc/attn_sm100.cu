@@ -55,11 +55,18 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct AttnParams {
   int s;          // sequence length
-  int bh;         // batch * heads
+  int bh;         // batch * heads computed by this launch
   int num_qblocks;
   int causal;
   float scale_log2;  // scale * log2(e)
-  int64_t row_stride;  // elements between consecutive rows of O (= D)
+  int bh_offset;     // first head of this launch inside the destination buffers
+  int num_dst;       // destination buffers (1 = local only)
+  int first_dst;     // destination served first, then round-robin
+};
+// One tensor map per destination buffer of O ([bh_total, S, D] bf16, box 64 d x 32 rows, 128-byte
+// swizzle): the local O, or with the all-gather folded in, every rank's O.
+struct AttnOutMaps {
+  CUtensorMap map[8];
 };
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -84,7 +91,7 @@ __device__ __forceinline__ int kv_blocks_for_tile(const AttnParams& p, int q0) {
 
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
-                const __grid_constant__ CUtensorMap tma_v, __nv_bfloat16* __restrict__ o, const AttnParams p,
+                const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ AttnOutMaps out_maps, const AttnParams p,
                 int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -360,26 +367,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tcgen05_fence_after();
+        // O = acc / l goes out through shared memory: this warp's 32 rows are converted, written in
+        // the 128-byte swizzle into the (now idle) shared memory of its own Q tile, and lane 0 issues
+        // one TMA store per 64-wide head-dim panel and destination.  Global (and NVLink) writes are
+        // full 128-byte lines, rows past the end of the sequence are clipped by the tensor map, and
+        // with several destinations this is the all-gather of O.
         const float inv_l = 1.0f / l;
-        __nv_bfloat16* dst = o + (static_cast<int64_t>(bh) * p.s + q_idx) * p.row_stride;
+        uint8_t* stage = smem + kSmemQ + t * kTileBytes + quarter * 32 * 128;  // + panel * kPanelBytes
+        const int row0 = q_base + t * kTileQ + quarter * 32;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t orow[32];
           tmem_ld_32x32b_x32(to + c * 32, orow);
           tcgen05_wait_ld();
-          if (q_idx < p.s) {
-            uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+          const uint32_t row_addr = smem_u32(stage + (c >> 1) * kPanelBytes) + lane * 128;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(orow[8 * i]) * inv_l, __uint_as_float(orow[8 * i + 1]) * inv_l);
-              v.y = pack_bf16x2(__uint_as_float(orow[8 * i + 2]) * inv_l, __uint_as_float(orow[8 * i + 3]) * inv_l);
-              v.z = pack_bf16x2(__uint_as_float(orow[8 * i + 4]) * inv_l, __uint_as_float(orow[8 * i + 5]) * inv_l);
-              v.w = pack_bf16x2(__uint_as_float(orow[8 * i + 6]) * inv_l, __uint_as_float(orow[8 * i + 7]) * inv_l);
-              d4[i] = v;
-            }
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t v0 = pack_bf16x2(__uint_as_float(orow[8 * i]) * inv_l, __uint_as_float(orow[8 * i + 1]) * inv_l);
+            const uint32_t v1 = pack_bf16x2(__uint_as_float(orow[8 * i + 2]) * inv_l, __uint_as_float(orow[8 * i + 3]) * inv_l);
+            const uint32_t v2 = pack_bf16x2(__uint_as_float(orow[8 * i + 4]) * inv_l, __uint_as_float(orow[8 * i + 5]) * inv_l);
+            const uint32_t v3 = pack_bf16x2(__uint_as_float(orow[8 * i + 6]) * inv_l, __uint_as_float(orow[8 * i + 7]) * inv_l);
+            const uint32_t unit = (c & 1) * 4 + i;  // 16-byte unit inside the 128-byte row
+            const uint32_t dst = row_addr + ((unit ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v0), "r"(v1), "r"(v2), "r"(v3) : "memory");
           }
         }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && row0 < p.s) {
+          int d = p.first_dst;
+          for (int i = 0; i < p.num_dst; ++i) {
+            tma_store_3d(&out_maps.map[d], stage, 0, row0, p.bh_offset + bh);
+            tma_store_3d(&out_maps.map[d], stage + kPanelBytes, 64, row0, p.bh_offset + bh);
+            if (++d == p.num_dst) d = 0;
+          }
+          tma_store_commit();
+          tma_store_wait_all<0>();
+        }
+        __syncwarp();
       }
     }
   }
@@ -400,12 +425,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 }  // namespace
 
 int attention_launch(const AttnProblem& a, cudaStream_t stream) {
-  if (!a.q || !a.k || !a.v || !a.o) return fail(SILE_ERR_INVALID, "attention: null buffer");
+  if (!a.q || !a.k || !a.v || (!a.o && a.num_peers == 0)) return fail(SILE_ERR_INVALID, "attention: null buffer");
+  if (a.num_peers < 0 || a.num_peers > 8) return fail(SILE_ERR_INVALID, "attention: at most 8 destinations");
   if (a.bh <= 0 || a.s <= 0) return fail(SILE_ERR_INVALID, "attention: non-positive dimension");
   if (a.d != kD) return fail(SILE_ERR_UNSUPPORTED, "attention: head_dim %lld not supported (128 only)", (long long)a.d);
   if (a.s > (1 << 24) || a.bh > (1 << 24)) return fail(SILE_ERR_INVALID, "attention: dimension too large");
   for (const void* ptr : {a.q, a.k, a.v, static_cast<const void*>(a.o)})
     if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(SILE_ERR_UNSUPPORTED, "attention: buffers must be 16-byte aligned");
+  for (int i = 0; i < a.num_peers; ++i)
+    if (!a.peer_o[i] || reinterpret_cast<uintptr_t>(a.peer_o[i]) % 16 != 0)
+      return fail(SILE_ERR_INVALID, "attention: destination %d is null or not 16-byte aligned", i);
+  if (a.num_peers > 0 && (a.bh_offset < 0 || a.bh_offset + a.bh > a.bh_total))
+    return fail(SILE_ERR_INVALID, "attention: heads [%lld, %lld) do not fit %lld", (long long)a.bh_offset, (long long)(a.bh_offset + a.bh), (long long)a.bh_total);
   if (!(a.scale > 0.0f)) return fail(SILE_ERR_INVALID, "attention: scale must be positive");
 
   // SILE_CUDA_ATTN_KERNEL=pair selects the CTA-pair kernel (attn_pair_sm100.cu): one Q tile per
@@ -414,7 +445,7 @@ int attention_launch(const AttnProblem& a, cudaStream_t stream) {
   // ~1200 when two warps share the MUFU pipe), which leaves it ~18 % behind this file's kernel;
   // that one stays the default.
   const char* which = std::getenv("SILE_CUDA_ATTN_KERNEL");
-  if (which && std::strcmp(which, "pair") == 0) return attention_pair_launch(a, stream);
+  if (which && std::strcmp(which, "pair") == 0 && a.num_peers == 0) return attention_pair_launch(a, stream);
 
   int* status = nullptr;
   if (int rc = device_status_word(&status)) return rc;
@@ -433,7 +464,21 @@ int attention_launch(const AttnProblem& a, cudaStream_t stream) {
   p.num_qblocks = static_cast<int>((a.s + kBlockQ - 1) / kBlockQ);
   p.causal = a.causal ? 1 : 0;
   p.scale_log2 = a.scale * 1.4426950408889634f;
-  p.row_stride = kD;
+  p.bh_offset = static_cast<int>(a.num_peers > 0 ? a.bh_offset : 0);
+  p.num_dst = a.num_peers > 0 ? a.num_peers : 1;
+  p.first_dst = a.num_peers > 0 ? a.peer_first : 0;
+
+  AttnOutMaps out_maps;
+  {
+    const uint64_t bh_total = static_cast<uint64_t>(a.num_peers > 0 ? a.bh_total : a.bh);
+    const uint64_t odims[3] = {static_cast<uint64_t>(kD), static_cast<uint64_t>(a.s), bh_total};
+    const uint32_t obox[3] = {64, 32, 1};
+    for (int i = 0; i < p.num_dst; ++i) {
+      void* base = a.num_peers > 0 ? a.peer_o[i] : a.o;
+      if (int rc = encode_tensor_map(&out_maps.map[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, odims, strides, obox, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+    }
+    for (int i = p.num_dst; i < 8; ++i) out_maps.map[i] = out_maps.map[0];
+  }
 
   static bool attr_set = false;
   if (!attr_set) {
@@ -442,7 +487,7 @@ int attention_launch(const AttnProblem& a, cudaStream_t stream) {
   }
   const int64_t grid = static_cast<int64_t>(p.bh) * p.num_qblocks;
   if (grid > 0x7fffffffll) return fail(SILE_ERR_INVALID, "attention: too many blocks");
-  attn_fwd_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, stream>>>(tq, tk, tv, static_cast<__nv_bfloat16*>(a.o), p, status);
+  attn_fwd_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, stream>>>(tq, tk, tv, out_maps, p, status);
   SILE_CUDA_TRY(cudaGetLastError());
   return SILE_OK;
 }

@@ -70,6 +70,13 @@ struct AttnProblem {
   int64_t bh = 0, s = 0, d = 0;
   float scale = 1.0f;
   int causal = 0;
+  // Fused all-gather of O: when num_peers > 0 the bh heads computed here are heads
+  // [bh_offset, bh_offset + bh) of peer_o[i] = rank i's [bh_total, S, D] buffer, and every rank's
+  // buffer receives them (o is ignored).  Otherwise O goes to `o` only.
+  int num_peers = 0;
+  int peer_first = 0;  // destination served first (the local rank), then round-robin
+  int64_t bh_total = 0, bh_offset = 0;
+  void* peer_o[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 int attention_launch(const AttnProblem& p, cudaStream_t stream);
 // CTA-pair kernel; arguments already validated by attention_launch.

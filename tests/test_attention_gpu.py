@@ -150,3 +150,25 @@ def test_a4_noncausal_b4_h32_s4096_sampled(sb, oracle):
 def test_a5_causal_shard_h32_s8192_sampled(sb, oracle):
     # one GPU's shard of the batch 8 x 32 heads configuration: 32 (batch, head) pairs
     _sampled_config(sb, oracle, 1, 32, 8192, True, 1)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_fused_allgather_epilogue_on_one_gpu(sb, attn_kernel, causal):
+    """sile_cuda_attention_allgather with the ranks played in turn on one GPU: every "rank" owns a
+    slab of heads and stores it into all destination buffers; afterwards each buffer must equal
+    the unsharded result.  (The entry point always runs the one-CTA kernel.)"""
+    import torch
+    if attn_kernel != "single":
+        pytest.skip("one pass is enough: the entry point does not depend on the kernel variant")
+    world, bh_local, s = 4, 3, 700
+    q, k, v = _inputs(world * bh_local, s, 128, 21)
+    want = torch.zeros_like(q)
+    sb.attention(q, k, v, want, 0.09, causal).apply()
+    bufs = [torch.full_like(q, 5.0) for _ in range(world)]
+    ptrs = [b.data_ptr() for b in bufs]
+    for r in range(world):
+        sl = slice(r * bh_local, (r + 1) * bh_local)
+        sb.attention_allgather(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), ptrs, r, 0.09, causal)
+    sb.synchronize()
+    for b in bufs:
+        assert torch.equal(b, want)
