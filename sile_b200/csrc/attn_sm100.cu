@@ -480,10 +480,10 @@ int attention_launch(const AttnProblem& a, cudaStream_t stream) {
     for (int i = p.num_dst; i < 8; ++i) out_maps.map[i] = out_maps.map[0];
   }
 
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[kMaxDevices] = {};
+  if (!attr_set[current_device_slot()]) {
     SILE_CUDA_TRY(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    attr_set = true;
+    attr_set[current_device_slot()] = true;
   }
   const int64_t grid = static_cast<int64_t>(p.bh) * p.num_qblocks;
   if (grid > 0x7fffffffll) return fail(SILE_ERR_INVALID, "attention: too many blocks");

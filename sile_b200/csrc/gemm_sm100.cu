@@ -834,10 +834,10 @@ EffectiveDims effective_dims(const GemmProblem& p) {
 template <typename OutT>
 int launch_typed(const CUtensorMap& ta, const CUtensorMap& tb, void* c, const GemmParams& gp, uint32_t idesc, int vec_ok,
                  int* status, int grid, cudaStream_t stream) {
-  static bool attr_set = false;  // per OutT instantiation
-  if (!attr_set) {
+  static bool attr_set[kMaxDevices] = {};  // per OutT instantiation and device
+  if (!attr_set[current_device_slot()]) {
     SILE_CUDA_TRY(cudaFuncSetAttribute(gemm_tn_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    attr_set = true;
+    attr_set[current_device_slot()] = true;
   }
   gemm_tn_kernel<OutT><<<grid, kNumThreads, kSmemBytes, stream>>>(ta, tb, static_cast<OutT*>(c), gp, idesc, vec_ok, status);
   SILE_CUDA_TRY(cudaGetLastError());
@@ -870,11 +870,15 @@ void pair_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int cluster
 }
 
 // Number of 2-CTA clusters of a pair kernel that can be resident at once (0 = clusters cannot
-// be scheduled on this device).  Queried once per kernel instantiation.
+// be scheduled on this device).  Queried once per kernel instantiation and device.
 template <typename OutT, bool kWide>
 int pair_max_clusters() {
-  static int max_clusters = -1;
-  if (max_clusters >= 0) return max_clusters;
+  static int cache[kMaxDevices];
+  static bool known[kMaxDevices] = {};
+  const int slot = current_device_slot();
+  if (known[slot]) return cache[slot];
+  known[slot] = true;
+  int& max_clusters = cache[slot];
   auto fn = PairKernel<OutT, kWide>::fn();
   if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, PairKernel<OutT, kWide>::smem) != cudaSuccess) {
     cudaGetLastError();

@@ -61,6 +61,15 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream);
 int unshard_columns_launch(void* dst, const void* src, int64_t parts, int64_t rows, int64_t cols, int elt_size,
                            cudaStream_t stream);
 
+// Per-device caches (function attributes, occupancy) are arrays indexed by this: one process may
+// drive several GPUs through sile_cuda_set_device.
+constexpr int kMaxDevices = 64;
+inline int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  return dev;
+}
+
 // ---- attention forward ----------------------------------------------------------
 struct AttnProblem {
   const void* q = nullptr;  // [BH, S, D] bf16
