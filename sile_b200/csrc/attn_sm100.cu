@@ -133,11 +133,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], kTileQ);
+      mbar_init(&p_full[i], 4);  // one arrival per softmax warp of the tile
       mbar_init(&o_done[i], 1);
     }
     fence_barrier_init();
     fence_proxy_async_smem();
+    // The first loads go out before the CTA-wide sync (this thread initialised the barriers they
+    // complete on), so they travel while tensor memory is being allocated.
+    auto load_first = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int row0) {
+      mbar_expect_tx(bar, kTileBytes);
+      tma_load_3d(dst, map, bar, 0, row0, bh);
+      tma_load_3d(dst + kPanelBytes, map, bar, 64, row0, bh);
+    };
+    if (n_kv[0] > 0) load_first(&tma_q, smem + kSmemQ, &q_full[0], q_base);
+    if (n_max > 0) load_first(&tma_k, smem + kSmemK, &k_full[0], 0);
+    if (n_kv[1] > 0) load_first(&tma_q, smem + kSmemQ + kTileBytes, &q_full[1], q_base + kTileQ);
+    if (n_max > 0) load_first(&tma_v, smem + kSmemV, &v_full[0], 0);
   }
   if (warp == 1) {
     tmem_alloc<1>(tmem_slot, kTmemCols);
@@ -159,10 +170,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         tma_load_3d(dst, map, bar, 0, row0, bh);
         tma_load_3d(dst + kPanelBytes, map, bar, 64, row0, bh);
       };
-      if (n_kv[0] > 0) load_tile(&tma_q, smem + kSmemQ, &q_full[0], q_base);
-      if (n_max > 0) load_tile(&tma_k, smem + kSmemK, &k_full[0], 0);
-      if (n_kv[1] > 0) load_tile(&tma_q, smem + kSmemQ + kTileBytes, &q_full[1], q_base + kTileQ);
-      if (n_max > 0) load_tile(&tma_v, smem + kSmemV, &v_full[0], 0);
+      // Q tiles and block 0 of K / V were requested before the CTA-wide sync above.
       for (int j = 1; j < n_max && ok; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -359,7 +367,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       l = l * alpha + (sum0 + sum1);
       tcgen05_wait_st();
       tcgen05_fence_before();
-      mbar_arrive(&p_full[t]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
     }
 
     if (ok && n > 0) {
