@@ -34,7 +34,7 @@ NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes (read + write) of one 8192^3 GEMM launch; from the ncu capture summarised in
 # profiles/gemm_tn_pair_wide_kernel_bf16_8192.md (dram__bytes_read.sum + dram__bytes_write.sum).
-GEMM_DRAM_TRAFFIC_BYTES = 1.040e9
+GEMM_DRAM_TRAFFIC_BYTES = 1.046e9
 ORACLE_TILE = (64, 64, 32)  # logical tile of the reference's GEMM example configuration
 # name -> (batch*heads, seq, causal) for attention; None for the f32 GEMM
 SIDE_WORKLOADS = {
