@@ -7,8 +7,8 @@
 // crates/sile-tile-ir/src/passes/lowering/tile_compute/mma.rs:25-260): online softmax over
 // 128-key blocks with the running row max m, row sum l and an unnormalised accumulator.
 //
-// One CTA = one (batch*head, 256-query block) = two 128-row Q tiles, 10 warps
-// (320 threads leave each softmax thread 200 registers for its 128 scores; 384 would cap it at 168):
+// One CTA = one (batch*head, 256-query block) = two 128-row Q tiles, 10 warps (ptxas gives each
+// thread 168 registers, enough for a softmax thread's 128 scores with a few bytes of spill):
 //   warp 0        TMA producer: Q tiles once, then K_j / V_j through 2-stage rings
 //   warp 1        MMA issuer:   S_t = Q_t K_j^T (smem x smem) and O_t += P_t V_j
 //                 (P_t read from TMEM, V_j MN-major from smem), f32 accumulators in TMEM.
@@ -20,7 +20,8 @@
 //   warps 6..9    softmax of Q tile 1
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 columns each; P_t (bf16 pairs) overwrites the
 // first 64 columns of S_t.  Per tile the chain is S -> softmax -> PV -> next S; the softmax of one
-// tile runs under the MMAs of the other.  O is rescaled only when the row max has grown by more
+// tile runs under the MMAs of the other, and P_t reaches the MMA warp in two pieces so that most
+// of P V runs under the last exponentials.  O is rescaled only when the row max has grown by more
 // than 2^8 since the last rescale; the same (stale) max is used for P and l, so the result is
 // unchanged.  The rescale and the final 1/l normalisation are done by the softmax warps.
 #include <cuda_bf16.h>
