@@ -460,6 +460,36 @@ def main():
                "returns its column block of C)",
     }
     e2e_check = float((c_h[:64].float() - c[:64, rank * nshard:(rank + 1) * nshard].float().cpu()).abs().max())
+    # What the host link alone allows: plain copies of the same pinned buffers, timed with CUDA
+    # events.  The inputs must all cross before the last rows of C can be computed, so the
+    # host->device time of A and B is a floor for one end-to-end step on this box.
+    scratch_in = torch.empty(a_h.numel() + b_h.numel(), dtype=torch.bfloat16, device=dev)
+    scratch_out = torch.empty(c_h.numel(), dtype=torch.bfloat16, device=dev)
+    c_back = torch.empty_like(c_h).pin_memory()
+
+    def timed_copy(fn):
+        best = float("inf")
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return best
+
+    def copy_in():
+        scratch_in[:a_h.numel()].copy_(a_h.view(-1), non_blocking=True)
+        scratch_in[a_h.numel():].copy_(b_h.view(-1), non_blocking=True)
+
+    h2d_ms = timed_copy(copy_in)
+    d2h_ms = timed_copy(lambda: c_back.view(-1).copy_(scratch_out, non_blocking=True))
+    e2e["host_link"] = {
+        "h2d_GBps": scratch_in.numel() * 2 / (h2d_ms * 1e-3) / 1e9, "d2h_GBps": scratch_out.numel() * 2 / (d2h_ms * 1e-3) / 1e9,
+        "inputs_h2d_ms": h2d_ms, "frac_of_step": h2d_ms / (e2e_s * 1e3),
+        "note": "plain pinned-memory copies of this rank's A and B (in) and C (out); the step cannot be shorter than inputs_h2d_ms",
+    }
+    del scratch_in, scratch_out, c_back
 
     # ---- side measurements (N = 1): attention forward and the f32 GEMM ----------------------------
     extras = {}

@@ -2,6 +2,7 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -317,15 +318,49 @@ int launch_host_matmul_pipelined(const SileKernelDesc* d, void* const* host, con
   const int64_t m = shapes[0], k = shapes[1], n = shapes[5];
   const int64_t bm = const_or_one(d, 0);
   if (d->in_dtype == SILE_DTYPE_F32 || d->b_layout != SILE_LAYOUT_COL_MAJOR) return SILE_OK;
-  int64_t rows = 1024;
-  while (rows % bm != 0 && rows < m) rows += 1024;   // chunk boundaries must fall on logical tile boundaries
+  // Rows per chunk: small chunks shorten the pipeline's fill and drain, large ones keep the GEMM
+  // efficient.  SILE_CUDA_HOST_CHUNK_ROWS overrides the default for tuning.
+  int64_t base_rows = 1024;
+  if (const char* env = std::getenv("SILE_CUDA_HOST_CHUNK_ROWS")) {
+    const long v = std::atol(env);
+    if (v >= 128 && v % 128 == 0) base_rows = v;
+  }
+  int64_t rows = base_rows;
+  while (rows % bm != 0 && rows < m) rows += base_rows;   // chunk boundaries must fall on logical tile boundaries
   if (m < 4 * rows || rows % bm != 0 || m % bm != 0 || static_cast<double>(m) * n * k < 1e11) return SILE_OK;
   *handled = true;
   const size_t in_sz = dtype_size(d->in_dtype), out_sz = dtype_size(d->out_dtype);
-  cudaStream_t s_in = nullptr, s_run = nullptr, s_out = nullptr;
-  SILE_CUDA_TRY(cudaStreamCreateWithFlags(&s_in, cudaStreamNonBlocking));
-  SILE_CUDA_TRY(cudaStreamCreateWithFlags(&s_run, cudaStreamNonBlocking));
-  SILE_CUDA_TRY(cudaStreamCreateWithFlags(&s_out, cudaStreamNonBlocking));
+  // The three streams are made once per host thread and device and reused by later calls.
+  struct Streams {
+    int device = -1;
+    cudaStream_t in = nullptr, run = nullptr, out = nullptr;
+  };
+  static thread_local Streams cached;
+  int dev_now = 0;
+  SILE_CUDA_TRY(cudaGetDevice(&dev_now));
+  if (cached.device != dev_now) {
+    cached = Streams{};
+    SILE_CUDA_TRY(cudaStreamCreateWithFlags(&cached.in, cudaStreamNonBlocking));
+    SILE_CUDA_TRY(cudaStreamCreateWithFlags(&cached.run, cudaStreamNonBlocking));
+    SILE_CUDA_TRY(cudaStreamCreateWithFlags(&cached.out, cudaStreamNonBlocking));
+    cached.device = dev_now;
+  }
+  cudaStream_t s_in = cached.in, s_run = cached.run, s_out = cached.out;
+  // Row chunks: full ones, then the last one halved down to 256 rows, so that what is left to do
+  // after the last input row has arrived (one GEMM and one copy back) is small.
+  std::vector<int64_t> chunk_rows;
+  {
+    int64_t left = m;
+    while (left > rows) {
+      chunk_rows.push_back(rows);
+      left -= rows;
+    }
+    while (left >= 512 && (left / 2) % bm == 0 && (left / 2) % 128 == 0) {
+      chunk_rows.push_back(left / 2);
+      left -= left / 2;
+    }
+    chunk_rows.push_back(left);
+  }
   void *da = nullptr, *db = nullptr, *dc = nullptr;
   std::vector<cudaEvent_t> events;
   int rc = SILE_OK;
@@ -344,8 +379,9 @@ int launch_host_matmul_pipelined(const SileKernelDesc* d, void* const* host, con
   check(cudaMallocAsync(&dc, static_cast<size_t>(m * n) * out_sz, s_in), "device allocation");
   if (rc == SILE_OK) {
     check(cudaMemcpyAsync(db, host[1], static_cast<size_t>(k * n) * in_sz, cudaMemcpyHostToDevice, s_in), "host->device copy");
-    for (int64_t r0 = 0; r0 < m && rc == SILE_OK; r0 += rows) {
-      const int64_t rc_rows = std::min(rows, m - r0);
+    int64_t r0 = 0;
+    for (size_t ci = 0; ci < chunk_rows.size() && rc == SILE_OK; r0 += chunk_rows[ci], ++ci) {
+      const int64_t rc_rows = chunk_rows[ci];
       const size_t a_off = static_cast<size_t>(r0 * k) * in_sz, c_off = static_cast<size_t>(r0 * n) * out_sz;
       check(cudaMemcpyAsync(static_cast<char*>(da) + a_off, static_cast<const char*>(host[0]) + a_off,
                             static_cast<size_t>(rc_rows * k) * in_sz, cudaMemcpyHostToDevice, s_in), "host->device copy");
@@ -376,9 +412,6 @@ int launch_host_matmul_pipelined(const SileKernelDesc* d, void* const* host, con
   cudaStreamSynchronize(s_in);
   for (cudaEvent_t ev : events)
     if (ev) cudaEventDestroy(ev);
-  cudaStreamDestroy(s_in);
-  cudaStreamDestroy(s_run);
-  cudaStreamDestroy(s_out);
   return rc;
 }
 
