@@ -115,7 +115,10 @@ int sile_cuda_launch(const SileKernelDesc* desc, void* const* dev_buffers, const
 /* Same launch with HOST buffers: stages inputs to the device, runs, copies
  * outputs (the last buffer; for relu the only buffer) back, and returns when
  * complete -- what MetalBackend::execute_llir does around its dispatch
- * (crates/sile-backend/src/metal/mod.rs:117-125,160-169). */
+ * (crates/sile-backend/src/metal/mod.rs:117-125,160-169).  Large 16-bit
+ * matmuls with a column-major B are streamed: B first, then A in row chunks
+ * (1024 rows; SILE_CUDA_HOST_CHUNK_ROWS overrides) whose GEMMs and copies back
+ * overlap the copies in; the streams used are kept per host thread. */
 int sile_cuda_launch_host(const SileKernelDesc* desc, void* const* host_buffers, const int64_t* shapes,
                           int64_t num_shapes, const uint32_t grid[3]);
 
