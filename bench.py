@@ -27,6 +27,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+_OUT = sys.stdout  # where the one JSON line goes; main() replaces it with the process's original stdout
 METRIC = "bf16 GEMM & flash-attn fwd TFLOPS per B200 (% of tensor peak), 1/2/4/8 GPU"
 UNIT = "TFLOP/s"
 GEMM_N = 8192
@@ -201,7 +202,7 @@ def run_reference(args, rank, world):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=_OUT, flush=True)
 
 
 def run_side_workload(name, iters, warmup, peaks):
@@ -265,7 +266,19 @@ def run_side_workload(name, iters, warmup, peaks):
 
 
 # ---------------------------------------------------------------------------------------------
+def _claim_stdout():
+    """Keeps stdout for the JSON line alone: file descriptor 1 is pointed at stderr for everything
+    else in the process (libraries such as NCCL print a version banner on it), and the returned
+    handle writes to the original stdout."""
+    sys.stdout.flush()
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return real
+
+
 def main():
+    global _OUT
+    _OUT = _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -309,7 +322,7 @@ def main():
             peaks, _ = load_peaks()
             res = run_side_workload(args.workload, args.steps, args.warmup, peaks)
             res.update({"workload": args.workload, "steps": args.steps, "warmup": args.warmup})
-            print(json.dumps(res), flush=True)
+            print(json.dumps(res), file=_OUT, flush=True)
         return
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}", file=sys.stderr)
@@ -598,7 +611,7 @@ def main():
     if rank == 0 and p == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline()
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=_OUT, flush=True)
     if p > 1:
         dist.barrier()
         dist.destroy_process_group()

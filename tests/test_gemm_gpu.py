@@ -235,11 +235,13 @@ def test_fused_allgather_epilogue_on_one_gpu(sb, oracle, world):
     assert torch.equal(single, bufs[0])      # sharding changes nothing, bit for bit
 
 
-def test_host_buffer_launch_pipelines_large_bf16_and_matches_device_launch(sb):
+@pytest.mark.parametrize("m", [4096, 4160, 4608])
+def test_host_buffer_launch_pipelines_large_bf16_and_matches_device_launch(sb, m):
     """sile_cuda_launch_host streams a large 16-bit matmul in row chunks (copy in / compute /
-    copy out overlapped); the result must equal the device-resident launch bit for bit."""
+    copy out overlapped; full 1024-row chunks, then a tapered tail: 512 + 256 + 256 rows, a
+    64-row remainder, or 256 + 256); the result must equal the device-resident launch bit for bit."""
     import torch
-    m, n, k = 4096, 4096, 8192
+    n, k = 4096, 8192
     g = torch.Generator().manual_seed(3)
     a = (torch.randn(m, k, generator=g) / k ** 0.5).to(torch.bfloat16).pin_memory()
     b = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16).pin_memory()  # [N, K]: column-major B
