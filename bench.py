@@ -138,15 +138,23 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------
+def bf16_round(x):
+    """float32 array -> nearest-even bf16 value, kept as float32 (what the oracle runs on)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = (u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)
+    return r.view(np.float32)
+
+
 def cpu_oracle_gemm_sample(num_tiles: int, seed: int = 0):
     """Times the CPU oracle (the plain-C port of the reference's generated matmul) on a seeded
     sample of logical 64x64 output tiles of the 8192^3 problem, all host cores."""
     import oracle
     o = oracle.load()
+    o.use_all_cores()
     n = GEMM_N
     rng = np.random.default_rng(seed)
-    a = (rng.standard_normal((n, n), dtype=np.float32) / np.float32(np.sqrt(n)))
-    b = (rng.standard_normal((n, n), dtype=np.float32) / np.float32(np.sqrt(n)))
+    a = bf16_round(rng.standard_normal((n, n), dtype=np.float32) / np.float32(np.sqrt(n)))
+    b = bf16_round(rng.standard_normal((n, n), dtype=np.float32) / np.float32(np.sqrt(n)))
     bm, bn, bk = ORACLE_TILE
     ids = rng.choice((n // bm) * (n // bn), size=num_tiles, replace=False)
     return o, a, b, ids

@@ -57,6 +57,14 @@ extern "C" {
 #define SILE_OP_PARALLEL_REDUCE 6 /* examples/parallel_reduce.rs:3-9 */
 #define SILE_OP_MATVEC 7          /* examples/mlp.rs:28-46 */
 
+/* SileKernelDesc.flags.
+ * SILE_FLAG_ACCUMULATE (matmul): the accumulator is seeded with the output tile instead of
+ * `constant(0.0, [BM, BN])`, i.e. C = C + A * B -- the reference's general mma `D = acc + A * B`
+ * with `sum0 = acc[r][c]` (crates/sile-tile-ir/src/passes/lowering/tile_compute/mma.rs:25-260),
+ * the path a kernel takes there when CanonicalMatmulPlan::detect refuses its non-zero seed
+ * (canonical_matmul.rs:446-666).  C is then an input as well as the output. */
+#define SILE_FLAG_ACCUMULATE 1
+
 /* C mirror of what sile_hir::Kernel (crates/sile-hir/src/kernel.rs:9-83) tells a
  * backend once its body has been recognised: which pattern, the const-generic
  * values the reference bakes into generated code, and the dtype/layout extensions. */
@@ -68,7 +76,7 @@ typedef struct SileKernelDesc {
   int32_t b_layout;     /* matmul: SILE_LAYOUT_* of B */
   int32_t causal;       /* attention: 1 = key index <= query index */
   float scale;          /* attention: softmax scale applied to Q*K^T */
-  int32_t reserved;
+  int32_t flags;        /* SILE_FLAG_* bits; 0 for the kernels of the reference's examples */
   int64_t consts[4];    /* matmul: BM,BN,BK; vec_add/parallel_reduce: TILE;
                            softmax: BM,BN; matvec: BM,BK; 0 = unspecified (treated as 1) */
 } SileKernelDesc;
@@ -84,6 +92,10 @@ typedef struct SileKernelDesc {
  * sile_cuda_last_status() / sile_cuda_last_error() and leave outputs untouched. */
 void sile_kernel_matmul(void** buffers, int64_t num_threadgroups, int64_t threads_per_group,
                         const int64_t* shapes, int64_t num_shapes);
+/* matmul whose accumulator starts from the output tile (SILE_FLAG_ACCUMULATE): buffers a, b, c
+ * with c read and written; const generics bound under the name "matmul_acc". */
+void sile_kernel_matmul_acc(void** buffers, int64_t num_threadgroups, int64_t threads_per_group,
+                            const int64_t* shapes, int64_t num_shapes);
 void sile_kernel_vec_add(void** buffers, int64_t num_threadgroups, int64_t threads_per_group,
                          const int64_t* shapes, int64_t num_shapes);
 void sile_kernel_relu(void** buffers, int64_t num_threadgroups, int64_t threads_per_group,
@@ -195,7 +207,11 @@ int sile_cuda_unshard_columns(void* dst, const void* src, int64_t parts, int64_t
  *
  * Asynchronous on `stream` when `wait` is 0.  With `wait` != 0 the call returns
  * after the stream has drained and reports SILE_ERR_TIMEOUT if a bounded
- * device-side wait ran out during this (or an earlier non-waiting) call. */
+ * device-side wait ran out during this (or an earlier non-waiting) call.  After
+ * non-waiting calls, sile_cuda_synchronize / sile_cuda_memcpy_d2h report and
+ * clear such a time-out too; until one of them (or a waiting call) has read it,
+ * every further launch on the device gives up at its first wait, so synchronise
+ * through this library before trusting results of a run of non-waiting calls. */
 int sile_cuda_matmul_f32_noalloc(const float* a, const float* b, float* c, int64_t m, int64_t n,
                                  int64_t k, int64_t bm, int64_t bn, int64_t bk, void* stream,
                                  int32_t wait);
@@ -207,8 +223,15 @@ int sile_cuda_device_count(void);
 
 /* Stream::synchronize (crates/sile-core/src/stream.rs:17-19), a no-op in the
  * reference, is real here.  Also reports a device-side time-out recorded since
- * the last call (SILE_ERR_TIMEOUT) and clears it. */
+ * the last call (SILE_ERR_TIMEOUT) by any launch of this library on the current
+ * device, sile_cuda_matmul_f32_noalloc included, and clears it. */
 int sile_cuda_synchronize(void* stream);
+
+/* The error a kernel's status word stands for: low byte = SILE_ERR_* code, bit 8 + n set = wait
+ * site n was stuck when the kernel gave up.  Records the message for sile_cuda_last_error() and
+ * returns the code; 0 maps to SILE_OK and leaves the last error alone.  Needs no device (the
+ * mapping the blocking entry points apply after reading the word back). */
+int sile_cuda_decode_status(int status_word);
 
 /* Device-resident tensors and real streams.  The reference's Tensor is a host Vec<f32> and every
  * GPU backend re-uploads it per launch (crates/sile/src/tensor.rs:5-9;
@@ -233,6 +256,14 @@ size_t sile_cuda_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int32_t
 /* Message / code of the calling thread's most recent failure ("" / SILE_OK if none). */
 const char* sile_cuda_last_error(void);
 int sile_cuda_last_status(void);
+
+/* The kernel the calling thread's most recent launch chose, with its geometry:
+ * "<kernel name> grid=<CTAs> block=<threads> smem=<bytes>" ("" before any launch).  The
+ * reference prints the generated source / IR of every launch to stderr under SILE_PRINT_SOURCE,
+ * SILE_PRINT_LLVMIR, SILE_PRINT_TILEIR (crates/sile/src/kernel_launcher.rs:11-13,48-53); with
+ * any of the three set this library prints the same line per launch instead -- its kernels are
+ * hand-written, so the choice and geometry are what there is to dump. */
+const char* sile_cuda_last_kernel(void);
 
 /* Library version: major*10000 + minor*100 + patch. */
 int sile_cuda_version(void);

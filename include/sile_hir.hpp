@@ -16,7 +16,11 @@
 // lower.rs:140-400) produces for the example of that name:
 //   matmul           crates/sile/examples/matmul.rs:3-18, mlp.rs:6-22; detection mirrors what
 //                    CanonicalMatmulPlan::detect requires of the tile IR
-//                    (crates/sile-tile-ir/src/passes/lowering/canonical_matmul.rs:446-666)
+//                    (crates/sile-tile-ir/src/passes/lowering/canonical_matmul.rs:446-666).
+//                    The same body with the accumulator seeded from the output tile
+//                    (`let mut acc = c.load_tile([BM, BN], [pid0, pid1])`) is the reference's
+//                    general `mma(a, b, acc)` (tile_compute/mma.rs:25-260) and maps to the
+//                    matmul with SILE_FLAG_ACCUMULATE; any other seed is refused
 //   vec_add          crates/sile/examples/vec_add.rs:3-13
 //   relu             crates/sile/examples/mlp.rs:51-55
 //   softmax          crates/sile/examples/softmax.rs:3-16
@@ -324,10 +328,22 @@ inline bool recognise_matmul(const hir::Kernel& k, SileKernelDesc* out) {
   Resolver r(k);
   const size_t loop_at = bind_lets(r, k.body);
   if (loop_at + 2 != k.body.size()) return false;  // lets, one loop, the store
-  // acc = constant(0.0, [BM, BN])
+  // acc = constant(0.0, [BM, BN])  -- the canonical matmul -- or
+  // acc = c.load_tile([BM, BN], [pid0, pid1])  -- the accumulator seeded with the output tile,
+  // which the reference lowers through its general mma (tile_compute/mma.rs:25-260)
   const Expr acc_init = r.resolve(Expr::Var(acc));
   int64_t bmn[2];
-  if (!is_op(acc_init, BuiltinOp::Constant, 2) || !is_zero_f32(acc_init.args[0]) || !const_dims(acc_init.args[1], 2, bmn)) return false;
+  bool seeded = false;
+  if (is_op(acc_init, BuiltinOp::Constant, 2)) {
+    if (!is_zero_f32(acc_init.args[0]) || !const_dims(acc_init.args[1], 2, bmn)) return false;
+  } else {
+    TileLoad lc;
+    if (!match_load(r, acc_init, 2, &lc) || lc.tensor != C) return false;
+    if (!is_program_id(lc.coords[0], 0) || !is_program_id(lc.coords[1], 1)) return false;
+    bmn[0] = lc.dims[0];
+    bmn[1] = lc.dims[1];
+    seeded = true;
+  }
   r.keep(acc);  // loop-carried from here on
   const Stmt& loop = k.body[loop_at];
   int64_t bk = 0;
@@ -346,6 +362,7 @@ inline bool recognise_matmul(const hir::Kernel& k, SileKernelDesc* out) {
   if (!is_program_id(la.coords[0], 0) || !is_var(la.coords[1], loop.name)) return false;
   if (!is_var(lb.coords[0], loop.name) || !is_program_id(lb.coords[1], 1)) return false;
   *out = make_desc(SILE_OP_MATMUL, {bmn[0], bmn[1], bk});
+  if (seeded) out->flags = SILE_FLAG_ACCUMULATE;
   return true;
 }
 

@@ -54,10 +54,12 @@ class Oracle:
         L.sile_oracle_bind_matvec.argtypes = [_i64] * 2
         fp = C.POINTER(C.c_float)
         L.sile_oracle_matmul.argtypes = [fp, fp, fp] + [_i64] * 7
+        L.sile_oracle_matmul_acc.argtypes = [fp, fp, fp] + [_i64] * 7
         L.sile_oracle_matmul_tiles.argtypes = [fp, fp, fp] + [_i64] * 6 + [C.POINTER(_i64), _i64]
         L.sile_oracle_attention.argtypes = [fp, fp, fp, fp] + [_i64] * 5 + [
             C.c_float, C.c_int, C.POINTER(_i64), _i64]
         L.sile_oracle_num_threads.restype = C.c_int
+        L.sile_oracle_set_num_threads.argtypes = [C.c_int]
 
     # -- exact-ABI launch, as the reference's CPU runtime performs it
     #    (crates/sile-backend/src/cpu/mod.rs:104-128)
@@ -71,6 +73,16 @@ class Oracle:
     def num_threads(self) -> int:
         return int(self.lib.sile_oracle_num_threads())
 
+    def use_all_cores(self) -> int:
+        """OpenMP threads = the cores this process may run on, whatever OMP_NUM_THREADS says
+        (process launchers such as torch.distributed.run export OMP_NUM_THREADS=1)."""
+        try:
+            n = len(os.sched_getaffinity(0))
+        except AttributeError:
+            n = os.cpu_count() or 1
+        self.lib.sile_oracle_set_num_threads(n)
+        return self.num_threads()
+
     def matmul(self, a, b, bm, bn, bk, grid=None):
         m, k = a.shape
         n = b.shape[1]
@@ -78,6 +90,15 @@ class Oracle:
         ntg = (m // bm) * (n // bn) if grid is None else int(np.prod(grid))
         self.lib.sile_oracle_matmul(_fptr(a), _fptr(b), _fptr(c), m, n, k, bm, bn, bk, ntg)
         return c
+
+    def matmul_acc(self, a, b, c, bm, bn, bk, grid=None):
+        """c + a @ b over whole logical tiles (accumulator seeded from c); returns a new array."""
+        m, k = a.shape
+        n = b.shape[1]
+        out = np.ascontiguousarray(c, dtype=np.float32).copy()
+        ntg = (m // bm) * (n // bn) if grid is None else int(np.prod(grid))
+        self.lib.sile_oracle_matmul_acc(_fptr(a), _fptr(b), _fptr(out), m, n, k, bm, bn, bk, ntg)
+        return out
 
     def matmul_tiles(self, a, b, bm, bn, bk, tile_ids):
         """Compute only the listed logical tiles; the rest of C stays zero."""

@@ -35,6 +35,9 @@ void sile_oracle_bind_parallel_reduce(int64_t tile) { g_pr_tile = tile; }
 void sile_oracle_bind_matvec(int64_t bm, int64_t bk) { g_mv_bm = bm; g_mv_bk = bk; }
 
 int sile_oracle_num_threads(void) { return omp_get_max_threads(); }
+/* The reference's runtime leaves the thread count to OpenMP's default (all cores); a launcher
+ * that exports OMP_NUM_THREADS=1 to its children would otherwise pin the baseline to one core. */
+void sile_oracle_set_num_threads(int n) { if (n > 0) omp_set_num_threads(n); }
 
 /* ---- GEMM: canonical whole-kernel pattern ------------------------------- */
 
@@ -257,6 +260,38 @@ static void tile_mma(const float* a, int64_t lda, const float* b, int64_t ldb,
         sum = sum + a[r * lda + kk] * b[kk * ldb + c];
       acc[r * ldacc + c] = sum;
     }
+}
+
+/* ---- matmul with the accumulator seeded from the output tile ----------------- */
+/* `let mut acc = c.load_tile([BM,BN],[pid0,pid1]); for k { acc = mma(a_k, b_k, acc) }; c.store(acc)`:
+ * the seed is not Splat(0), so CanonicalMatmulPlan::detect (canonical_matmul.rs:446-666)
+ * refuses the body and every k step runs the general tile mma, whose sums start from acc[r][c]
+ * (tile_compute/mma.rs:25-260), on tiles copied into private arrays (tile_memory.rs:22-162). */
+void sile_oracle_matmul_acc(const float* a, const float* b, float* c, int64_t m,
+                            int64_t n, int64_t k, int64_t bm, int64_t bn,
+                            int64_t bk, int64_t num_threadgroups) {
+  const int64_t tiles_n = n / bn;
+  const int64_t total_tiles = (m / bm) * tiles_n;
+#pragma omp parallel for schedule(static)
+  for (int64_t tg = 0; tg < num_threadgroups; ++tg) {
+    if (tg >= total_tiles) continue;
+    const int64_t p0 = tg / tiles_n, p1 = tg % tiles_n;
+    float* acc = (float*)malloc(sizeof(float) * bm * bn);
+    float* at = (float*)malloc(sizeof(float) * bm * bk);
+    float* bt = (float*)malloc(sizeof(float) * bk * bn);
+    for (int64_t r = 0; r < bm; ++r)
+      for (int64_t cc = 0; cc < bn; ++cc) acc[r * bn + cc] = c[(p0 * bm + r) * n + p1 * bn + cc];
+    for (int64_t kt = 0; kt < k / bk; ++kt) {
+      for (int64_t r = 0; r < bm; ++r)
+        for (int64_t kk = 0; kk < bk; ++kk) at[r * bk + kk] = a[(p0 * bm + r) * k + kt * bk + kk];
+      for (int64_t kk = 0; kk < bk; ++kk)
+        for (int64_t cc = 0; cc < bn; ++cc) bt[kk * bn + cc] = b[(kt * bk + kk) * n + p1 * bn + cc];
+      tile_mma(at, bk, bt, bn, acc, bn, bm, bn, bk);
+    }
+    for (int64_t r = 0; r < bm; ++r)
+      for (int64_t cc = 0; cc < bn; ++cc) c[(p0 * bm + r) * n + p1 * bn + cc] = acc[r * bn + cc];
+    free(acc); free(at); free(bt);
+  }
 }
 
 static void attention_unit(const float* q, const float* kt, const float* v,

@@ -67,6 +67,13 @@ void sile_oracle_matmul_tiles(const float* a, const float* b, float* c,
                               int64_t bn, int64_t bk, const int64_t* tile_ids,
                               int64_t num_tiles);
 
+/* Matmul whose accumulator is seeded with the output tile, C = C + A*B through the general
+ * tile mma (tile_compute/mma.rs:25-260) -- the path the reference takes when the canonical
+ * pattern does not match.  c is read and written in place. */
+void sile_oracle_matmul_acc(const float* a, const float* b, float* c, int64_t m,
+                            int64_t n, int64_t k, int64_t bm, int64_t bn,
+                            int64_t bk, int64_t num_threadgroups);
+
 /* Attention forward composed from the reference's tile ops (general mma path,
  * left-fold reductions, expf).  q,o: [bh*s, d]; kt: [bh*d, s] (K supplied
  * transposed, the DSL has no transpose op); v: [bh*s, d]; all f32 row-major.
@@ -78,6 +85,7 @@ void sile_oracle_attention(const float* q, const float* kt, const float* v,
                            const int64_t* units, int64_t num_units);
 
 int sile_oracle_num_threads(void);
+void sile_oracle_set_num_threads(int n);
 
 #ifdef __cplusplus
 }

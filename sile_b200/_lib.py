@@ -11,18 +11,19 @@ from .build import LIB_PATH
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_NO_DEVICE = range(6)
 DTYPE_F32, DTYPE_BF16, DTYPE_F16 = 0, 1, 2
 LAYOUT_ROW_MAJOR, LAYOUT_COL_MAJOR = 0, 1
+FLAG_ACCUMULATE = 1
 OP_MATMUL, OP_ATTENTION, OP_VEC_ADD, OP_RELU, OP_SOFTMAX, OP_PARALLEL_REDUCE, OP_MATVEC = range(1, 8)
 
 # Every symbol include/sile_cuda.h declares.
 EXPORTED_SYMBOLS = (
-    "sile_kernel_matmul", "sile_kernel_vec_add", "sile_kernel_relu", "sile_kernel_softmax",
+    "sile_kernel_matmul", "sile_kernel_matmul_acc", "sile_kernel_vec_add", "sile_kernel_relu", "sile_kernel_softmax",
     "sile_kernel_parallel_reduce", "sile_kernel_matvec", "sile_cuda_bind_consts",
     "sile_cuda_launch", "sile_cuda_launch_host", "sile_cuda_matmul_shard",
     "sile_cuda_matmul_allgather", "sile_cuda_attention_allgather", "sile_cuda_unshard_columns", "sile_cuda_matmul_f32_noalloc", "sile_cuda_set_device",
-    "sile_cuda_device_count", "sile_cuda_synchronize", "sile_cuda_malloc", "sile_cuda_free",
+    "sile_cuda_device_count", "sile_cuda_synchronize", "sile_cuda_decode_status", "sile_cuda_malloc", "sile_cuda_free",
     "sile_cuda_memcpy_h2d", "sile_cuda_memcpy_d2h", "sile_cuda_memset", "sile_cuda_stream_create",
     "sile_cuda_stream_destroy", "sile_cuda_matmul_workspace_bytes",
-    "sile_cuda_last_error", "sile_cuda_last_status", "sile_cuda_version",
+    "sile_cuda_last_error", "sile_cuda_last_status", "sile_cuda_last_kernel", "sile_cuda_version",
 )
 
 
@@ -31,7 +32,7 @@ class KernelDesc(C.Structure):
     _fields_ = [
         ("struct_size", C.c_uint32), ("op", C.c_int32), ("in_dtype", C.c_int32),
         ("out_dtype", C.c_int32), ("b_layout", C.c_int32), ("causal", C.c_int32),
-        ("scale", C.c_float), ("reserved", C.c_int32), ("consts", C.c_int64 * 4),
+        ("scale", C.c_float), ("flags", C.c_int32), ("consts", C.c_int64 * 4),
     ]
 
 
@@ -69,6 +70,7 @@ def lib() -> C.CDLL:
     L.sile_cuda_matmul_f32_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [_i64] * 6 + [C.c_void_p, C.c_int32]
     L.sile_cuda_set_device.argtypes = [C.c_int]
     L.sile_cuda_synchronize.argtypes = [C.c_void_p]
+    L.sile_cuda_decode_status.argtypes = [C.c_int]
     L.sile_cuda_malloc.argtypes = [C.POINTER(C.c_void_p), C.c_size_t]
     L.sile_cuda_free.argtypes = [C.c_void_p]
     L.sile_cuda_memcpy_h2d.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
@@ -79,5 +81,6 @@ def lib() -> C.CDLL:
     L.sile_cuda_matmul_workspace_bytes.argtypes = [_i64, _i64, _i64, C.c_int32]
     L.sile_cuda_matmul_workspace_bytes.restype = C.c_size_t
     L.sile_cuda_last_error.restype = C.c_char_p
+    L.sile_cuda_last_kernel.restype = C.c_char_p
     _lib = L
     return L

@@ -35,11 +35,11 @@ def _dtype_code(t) -> int:
 
 
 def make_desc(op: int, in_dtype=DTYPE_F32, out_dtype=DTYPE_F32, b_layout=LAYOUT_ROW_MAJOR,
-              causal=False, scale=1.0, consts: Sequence[int] = ()) -> KernelDesc:
+              causal=False, scale=1.0, consts: Sequence[int] = (), flags: int = 0) -> KernelDesc:
     d = KernelDesc()
     d.struct_size = C.sizeof(KernelDesc)
     d.op, d.in_dtype, d.out_dtype, d.b_layout = op, in_dtype, out_dtype, b_layout
-    d.causal, d.scale = int(bool(causal)), float(scale)
+    d.causal, d.scale, d.flags = int(bool(causal)), float(scale), int(flags)
     for i, v in enumerate(consts):
         d.consts[i] = int(v)
     return d
@@ -85,10 +85,12 @@ def _full_grid(m, n, bm, bn):
     return (max(m // bm, 1), max(n // bn, 1), 1)
 
 
-def matmul(a, b, c, bm=1, bn=1, bk=1, b_layout=LAYOUT_ROW_MAJOR) -> KernelLauncher:
+def matmul(a, b, c, bm=1, bn=1, bk=1, b_layout=LAYOUT_ROW_MAJOR, accumulate=False) -> KernelLauncher:
     """``matmul::<BM,BN,BK>(&a, &b, &mut c)`` (crates/sile/examples/matmul.rs:3-18).
 
-    With ``b_layout=LAYOUT_COL_MAJOR`` ``b`` is given as an [N, K] row-major tensor."""
+    With ``b_layout=LAYOUT_COL_MAJOR`` ``b`` is given as an [N, K] row-major tensor.  With
+    ``accumulate`` the accumulator is seeded with ``c``'s tile (``c = c + a @ b``), the general
+    ``mma(a, b, acc)`` of crates/sile-tile-ir/src/passes/lowering/tile_compute/mma.rs:25-260."""
     import torch
     if b_layout == LAYOUT_COL_MAJOR:
         # the ABI carries logical shapes: b is [K, N]
@@ -103,7 +105,8 @@ def matmul(a, b, c, bm=1, bn=1, bk=1, b_layout=LAYOUT_ROW_MAJOR) -> KernelLaunch
         b_arg = b
     in_dt = _dtype_code(a) if isinstance(a, torch.Tensor) else DTYPE_F32
     out_dt = _dtype_code(c) if isinstance(c, torch.Tensor) else DTYPE_F32
-    desc = make_desc(OP_MATMUL, in_dt, out_dt, b_layout, consts=(bm, bn, bk))
+    desc = make_desc(OP_MATMUL, in_dt, out_dt, b_layout, consts=(bm, bn, bk),
+                     flags=_lib.FLAG_ACCUMULATE if accumulate else 0)
     kl = KernelLauncher(desc, [a, b_arg, c])
     return kl.grid(_full_grid(c.shape[0], c.shape[1], bm, bn))
 

@@ -19,6 +19,7 @@ thread_local int t_last_status = SILE_OK;
 // Const generics bound for the exact-ABI entry points, per calling thread.
 struct BoundConsts {
   int64_t matmul[3] = {1, 1, 1};
+  int64_t matmul_acc[3] = {1, 1, 1};
   int64_t vec_add[1] = {4};  // the tile the reference's example hard-codes (examples/vec_add.rs:6)
   int64_t softmax[2] = {1, 0};  // BN = 0: whole row
   int64_t parallel_reduce[1] = {1};
@@ -28,6 +29,11 @@ thread_local BoundConsts t_consts;
 
 std::mutex g_status_mutex;
 int* g_status_words[64] = {nullptr};
+constexpr int kWorkCounters = 1024;
+int* g_work_counters[64] = {nullptr};
+unsigned g_work_counter_next[64] = {0};
+
+thread_local char t_last_kernel[160] = "";
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -68,6 +74,12 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+int decode_status_word(int word) {
+  if (word == 0) return SILE_OK;
+  return fail(word & 0xff, "a device-side wait ran out (code %d, stuck wait sites 0x%x); results of the affected launch are invalid",
+              word & 0xff, static_cast<unsigned>(word) >> 8);
+}
+
 int device_status_word(int** out) {
   int dev = 0;
   SILE_CUDA_TRY(cudaGetDevice(&dev));
@@ -81,6 +93,55 @@ int device_status_word(int** out) {
   }
   *out = g_status_words[dev];
   return SILE_OK;
+}
+
+// Staging buffers and workspaces come from a memory pool of the library's own (one per device),
+// which keeps what is freed for the next call; the application's default pool is left alone.
+cudaMemPool_t g_pools[64] = {nullptr};
+
+int pool_alloc(void** ptr, size_t bytes, cudaStream_t stream) {
+  int dev = 0;
+  SILE_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(SILE_ERR_INVALID, "device index %d out of range", dev);
+  cudaMemPool_t pool = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    if (!g_pools[dev]) {
+      cudaMemPoolProps props = {};
+      props.allocType = cudaMemAllocationTypePinned;
+      props.handleTypes = cudaMemHandleTypeNone;
+      props.location.type = cudaMemLocationTypeDevice;
+      props.location.id = dev;
+      SILE_CUDA_TRY(cudaMemPoolCreate(&g_pools[dev], &props));
+      uint64_t keep = UINT64_MAX;
+      SILE_CUDA_TRY(cudaMemPoolSetAttribute(g_pools[dev], cudaMemPoolAttrReleaseThreshold, &keep));
+    }
+    pool = g_pools[dev];
+  }
+  cudaError_t e = cudaMallocFromPoolAsync(ptr, bytes, pool, stream);
+  if (e != cudaSuccess) return fail(SILE_ERR_CUDA, "device allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+  return SILE_OK;
+}
+
+int device_work_counter(int** out) {
+  int dev = 0;
+  SILE_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(SILE_ERR_INVALID, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (!g_work_counters[dev]) {
+    int* p = nullptr;
+    SILE_CUDA_TRY(cudaMalloc(&p, kWorkCounters * sizeof(int)));
+    SILE_CUDA_TRY(cudaMemset(p, 0, kWorkCounters * sizeof(int)));
+    g_work_counters[dev] = p;
+  }
+  *out = g_work_counters[dev] + (g_work_counter_next[dev]++ % kWorkCounters);
+  return SILE_OK;
+}
+
+void note_kernel(const char* name, unsigned grid, unsigned block, size_t smem_bytes) {
+  snprintf(t_last_kernel, sizeof(t_last_kernel), "%s grid=%u block=%u smem=%zu", name, grid, block, smem_bytes);
+  static const bool print = std::getenv("SILE_PRINT_SOURCE") || std::getenv("SILE_PRINT_LLVMIR") || std::getenv("SILE_PRINT_TILEIR");
+  if (print) fprintf(stderr, "[sile_cuda] launch %s\n", t_last_kernel);
 }
 
 int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank, const void* base, const uint64_t* dims,
@@ -151,7 +212,8 @@ int describe_args(const SileKernelDesc* d, const int64_t* shapes, int64_t ns, in
       // tiles or a short grid): untouched elements must survive the round trip.
       const int64_t bm = const_or_one(d, 0), bn = const_or_one(d, 1);
       const bool partial = (m % bm) || (n % bn) || (ntg < (m / bm) * (n / bn));
-      out->push_back({static_cast<size_t>(m * n) * out_sz, partial, true});
+      const bool seeded = (d->flags & SILE_FLAG_ACCUMULATE) != 0;  // C is read: D = C + A * B
+      out->push_back({static_cast<size_t>(m * n) * out_sz, partial || seeded, true});
       return SILE_OK;
     }
     case SILE_OP_ATTENTION: {
@@ -220,10 +282,11 @@ int launch_device(const SileKernelDesc* d, void* const* buf, const int64_t* shap
       p.in_dtype = d->in_dtype; p.out_dtype = d->out_dtype; p.b_layout = d->b_layout;
       p.bm = const_or_one(d, 0); p.bn = const_or_one(d, 1); p.bk = const_or_one(d, 2);
       p.num_threadgroups = ntg;
+      p.accumulate = (d->flags & SILE_FLAG_ACCUMULATE) != 0;
       const size_t ws = gemm_workspace_bytes(p);
       void* wsp = nullptr;
       if (ws) {
-        SILE_CUDA_TRY(cudaMallocAsync(&wsp, ws, stream));
+        if (int rc = pool_alloc(&wsp, ws, stream)) return rc;
         p.workspace = wsp;
         p.workspace_bytes = ws;
       }
@@ -295,17 +358,18 @@ int validate_desc(const SileKernelDesc* d) {
   return SILE_OK;
 }
 
+// Reads and clears both per-device status words: the one every ordinary launch reports to and
+// the one inside the library image that the allocation-free matmul uses.  Either may hold a
+// time-out from an earlier asynchronous launch; the first one found is reported.
 int read_and_clear_status() {
   int* word = nullptr;
   if (int rc = device_status_word(&word)) return rc;
   int v = 0;
   SILE_CUDA_TRY(cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost));
-  if (v != 0) {
-    SILE_CUDA_TRY(cudaMemset(word, 0, sizeof(int)));
-    return fail(v & 0xff, "a device-side wait ran out (code %d, stuck wait sites 0x%x); results of the affected launch are invalid",
-                v & 0xff, static_cast<unsigned>(v) >> 8);
-  }
-  return SILE_OK;
+  if (v != 0) SILE_CUDA_TRY(cudaMemset(word, 0, sizeof(int)));
+  int v2 = 0;
+  if (int rc = noalloc_read_and_clear_status(&v2)) return rc;
+  return decode_status_word(v != 0 ? v : v2);
 }
 
 // Large 16-bit matmuls from host memory: A travels in row chunks on one stream, each chunk's
@@ -374,9 +438,9 @@ int launch_host_matmul_pipelined(const SileKernelDesc* d, void* const* host, con
     events.push_back(ev);
     return ev;
   };
-  check(cudaMallocAsync(&da, static_cast<size_t>(m * k) * in_sz, s_in), "device allocation");
-  check(cudaMallocAsync(&db, static_cast<size_t>(k * n) * in_sz, s_in), "device allocation");
-  check(cudaMallocAsync(&dc, static_cast<size_t>(m * n) * out_sz, s_in), "device allocation");
+  if (rc == SILE_OK) rc = pool_alloc(&da, static_cast<size_t>(m * k) * in_sz, s_in);
+  if (rc == SILE_OK) rc = pool_alloc(&db, static_cast<size_t>(k * n) * in_sz, s_in);
+  if (rc == SILE_OK) rc = pool_alloc(&dc, static_cast<size_t>(m * n) * out_sz, s_in);
   if (rc == SILE_OK) {
     check(cudaMemcpyAsync(db, host[1], static_cast<size_t>(k * n) * in_sz, cudaMemcpyHostToDevice, s_in), "host->device copy");
     int64_t r0 = 0;
@@ -421,17 +485,6 @@ int launch_host(const SileKernelDesc* d, void* const* host, const int64_t* shape
   if (!host || !shapes) return fail(SILE_ERR_INVALID, "null argument");
   std::vector<ArgSpan> args;
   if (int rc = describe_args(d, shapes, ns, ntg, &args)) return rc;
-  static thread_local int pool_dev = -1;
-  int cur_dev = 0;
-  SILE_CUDA_TRY(cudaGetDevice(&cur_dev));
-  if (pool_dev != cur_dev) {
-    // keep freed staging buffers in the stream-ordered pool between calls
-    cudaMemPool_t pool;
-    SILE_CUDA_TRY(cudaDeviceGetDefaultMemPool(&pool, cur_dev));
-    uint64_t keep = UINT64_MAX;
-    SILE_CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
-    pool_dev = cur_dev;
-  }
   if (d->op == SILE_OP_MATMUL && !args[2].is_input && host[0] && host[1] && host[2]) {
     bool handled = false;
     const int rc = launch_host_matmul_pipelined(d, host, shapes, &handled);
@@ -452,10 +505,10 @@ int launch_host(const SileKernelDesc* d, void* const* host, const int64_t* shape
   };
   for (size_t i = 0; i < args.size() && rc == SILE_OK; ++i) {
     if (!host[i]) { rc = fail(SILE_ERR_INVALID, "null buffer %zu", i); break; }
-    cudaError_t e = cudaMallocAsync(&dev[i], std::max<size_t>(args[i].bytes, 16), stream);
-    if (e != cudaSuccess) { rc = fail(SILE_ERR_CUDA, "device allocation of %zu bytes failed: %s", args[i].bytes, cudaGetErrorString(e)); break; }
+    rc = pool_alloc(&dev[i], std::max<size_t>(args[i].bytes, 16), stream);
+    if (rc != SILE_OK) break;
     if (args[i].is_input) {
-      e = cudaMemcpyAsync(dev[i], host[i], args[i].bytes, cudaMemcpyHostToDevice, stream);
+      cudaError_t e = cudaMemcpyAsync(dev[i], host[i], args[i].bytes, cudaMemcpyHostToDevice, stream);
       if (e != cudaSuccess) rc = fail(SILE_ERR_CUDA, "host->device copy failed: %s", cudaGetErrorString(e));
     }
   }
@@ -502,7 +555,10 @@ extern "C" {
 int sile_cuda_version(void) { return 100; }
 
 const char* sile_cuda_last_error(void) { return t_last_error.c_str(); }
+const char* sile_cuda_last_kernel(void) { return t_last_kernel; }
 int sile_cuda_last_status(void) { return t_last_status; }
+
+int sile_cuda_decode_status(int status_word) { return decode_status_word(status_word); }
 
 int sile_cuda_device_count(void) {
   int n = 0;
@@ -599,6 +655,7 @@ int sile_cuda_bind_consts(const char* name, const int64_t* consts, int64_t n) {
     return SILE_OK;
   };
   if (!std::strcmp(name, "matmul") || !std::strcmp(name, "gemm")) return set(t_consts.matmul, 3);
+  if (!std::strcmp(name, "matmul_acc")) return set(t_consts.matmul_acc, 3);
   if (!std::strcmp(name, "vec_add")) return set(t_consts.vec_add, 1);
   if (!std::strcmp(name, "softmax")) return set(t_consts.softmax, 2);
   if (!std::strcmp(name, "parallel_reduce")) return set(t_consts.parallel_reduce, 1);
@@ -710,6 +767,12 @@ int sile_cuda_unshard_columns(void* dst, const void* src, int64_t parts, int64_t
 void sile_kernel_matmul(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {
   SileKernelDesc d = f32_desc(SILE_OP_MATMUL);
   for (int i = 0; i < 3; ++i) d.consts[i] = t_consts.matmul[i];
+  launch_host(&d, buffers, shapes, num_shapes, num_threadgroups * threads_per_group);
+}
+void sile_kernel_matmul_acc(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {
+  SileKernelDesc d = f32_desc(SILE_OP_MATMUL);
+  d.flags = SILE_FLAG_ACCUMULATE;
+  for (int i = 0; i < 3; ++i) d.consts[i] = t_consts.matmul_acc[i];
   launch_host(&d, buffers, shapes, num_shapes, num_threadgroups * threads_per_group);
 }
 void sile_kernel_vec_add(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {

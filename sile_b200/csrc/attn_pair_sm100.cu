@@ -430,6 +430,7 @@ int attention_pair_launch(const AttnProblem& a, cudaStream_t stream) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_fwd_pair_kernel, tq, tk, tv, static_cast<__nv_bfloat16*>(a.o), p, status));
+  note_kernel("attn_fwd_pair_kernel", cfg.gridDim.x, cfg.blockDim.x, cfg.dynamicSmemBytes);
   return SILE_OK;
 }
 

@@ -472,13 +472,16 @@ int attention_launch(const AttnProblem& a, cudaStream_t stream) {
     return fail(SILE_ERR_INVALID, "attention: heads [%lld, %lld) do not fit %lld", (long long)a.bh_offset, (long long)(a.bh_offset + a.bh), (long long)a.bh_total);
   if (!(a.scale > 0.0f)) return fail(SILE_ERR_INVALID, "attention: scale must be positive");
 
-  // SILE_CUDA_ATTN_KERNEL=pair selects the CTA-pair kernel (attn_pair_sm100.cu): one Q tile per
-  // SM, K / V shared by the pair, three S buffers so the softmax never waits for the tensor core.
-  // Its single softmax warp per scheduler is latency-bound (~1500 cycles per 128 keys against
-  // ~1200 when two warps share the MUFU pipe), which leaves it ~18 % behind this file's kernel;
-  // that one stays the default.
+  // Kernel choice.  The default is this file's kernel, one CTA per (head, 256-query block).
+  // SILE_CUDA_ATTN_KERNEL=persistent selects the persistent kernel (attn_persist_sm100.cu: one
+  // CTA per SM walking a queue of items, the next item's first Q K^T issued under the current
+  // item's epilogue; measured 2-4 % behind on 4096- and 8192-long sequences, level at 1024),
+  // =pair the CTA-pair kernel (attn_pair_sm100.cu: one Q tile per SM, K / V shared by the pair,
+  // three S buffers; its single softmax warp per scheduler is latency-bound, ~18 % behind).
+  // Read on every launch.
   const char* which = std::getenv("SILE_CUDA_ATTN_KERNEL");
   if (which && std::strcmp(which, "pair") == 0 && a.num_peers == 0) return attention_pair_launch(a, stream);
+  if (which && std::strcmp(which, "persistent") == 0) return attention_persistent_launch(a, stream);
 
   int* status = nullptr;
   if (int rc = device_status_word(&status)) return rc;
@@ -522,6 +525,7 @@ int attention_launch(const AttnProblem& a, cudaStream_t stream) {
   if (grid > 0x7fffffffll) return fail(SILE_ERR_INVALID, "attention: too many blocks");
   attn_fwd_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, stream>>>(tq, tk, tv, out_maps, p, status);
   SILE_CUDA_TRY(cudaGetLastError());
+  note_kernel("attn_fwd_kernel", static_cast<unsigned>(grid), kThreads, kSmemBytes);
   return SILE_OK;
 }
 

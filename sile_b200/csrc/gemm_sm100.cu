@@ -63,6 +63,10 @@ struct GemmParams {
   long long ntg;
   int masked;  // 1 if the logical launch mask can exclude anything
   int group_m;  // 128-row blocks per raster group
+  // 1: the accumulator is seeded with the output tile, D = C + A * B -- the general mma of the
+  // reference (`sum0 = acc[r][c]`, tile_compute/mma.rs:25-260) with acc loaded from the output;
+  // the epilogue adds the value C held to the tensor-core sum before storing.
+  int accumulate;
 };
 
 // Destinations of the wide kernel's epilogue.  Normally one (the caller's C); for the fused
@@ -98,24 +102,51 @@ __device__ __forceinline__ void store_chunk(OutT* c, const GemmParams& p, int ro
     if constexpr (sizeof(OutT) == 4) {
       float4* dst = reinterpret_cast<float4*>(c + static_cast<int64_t>(row) * p.ldc + col0);
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
-                             __uint_as_float(r[4 * i + 3]));
+      for (int i = 0; i < 8; ++i) {
+        float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
+                               __uint_as_float(r[4 * i + 3]));
+        if (p.accumulate) {
+          const float4 old = dst[i];
+          v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+        }
+        dst[i] = v;
+      }
     } else {
       uint4* dst = reinterpret_cast<uint4*>(c + static_cast<int64_t>(row) * p.ldc + col0);
+      float f[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+      if (p.accumulate) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 old = dst[i];
+          const uint32_t w[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+              f[8 * i + 2 * h] += __uint_as_float(w[h] << 16);
+              f[8 * i + 2 * h + 1] += __uint_as_float(w[h] & 0xffff0000u);
+            } else {
+              const __half2 hv = *reinterpret_cast<const __half2*>(&w[h]);
+              f[8 * i + 2 * h] += __low2float(hv);
+              f[8 * i + 2 * h + 1] += __high2float(hv);
+            }
+          }
+        }
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         uint4 v;
         if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
-          v.x = pack_bf16x2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]));
-          v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-          v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-          v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+          v.x = pack_bf16x2(f[8 * i], f[8 * i + 1]);
+          v.y = pack_bf16x2(f[8 * i + 2], f[8 * i + 3]);
+          v.z = pack_bf16x2(f[8 * i + 4], f[8 * i + 5]);
+          v.w = pack_bf16x2(f[8 * i + 6], f[8 * i + 7]);
         } else {
-          __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]));
-          __half2 h1 = __floats2half2_rn(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-          __half2 h2 = __floats2half2_rn(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-          __half2 h3 = __floats2half2_rn(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+          __half2 h0 = __floats2half2_rn(f[8 * i], f[8 * i + 1]);
+          __half2 h1 = __floats2half2_rn(f[8 * i + 2], f[8 * i + 3]);
+          __half2 h2 = __floats2half2_rn(f[8 * i + 4], f[8 * i + 5]);
+          __half2 h3 = __floats2half2_rn(f[8 * i + 6], f[8 * i + 7]);
           v.x = *reinterpret_cast<uint32_t*>(&h0);
           v.y = *reinterpret_cast<uint32_t*>(&h1);
           v.z = *reinterpret_cast<uint32_t*>(&h2);
@@ -132,8 +163,13 @@ __device__ __forceinline__ void store_chunk(OutT* c, const GemmParams& p, int ro
   for (int i = 0; i < 32; ++i) {
     const int col = col0 + i;
     if (col < p.n_valid && (!p.masked || tile_row + col / p.lbn < p.ntg)) {
-      const float v = __uint_as_float(r[i]);
+      float v = __uint_as_float(r[i]);
       OutT* dst = c + static_cast<int64_t>(row) * p.ldc + col;
+      if (p.accumulate) {
+        if constexpr (sizeof(OutT) == 4) v += *dst;
+        else if constexpr (std::is_same<OutT, __nv_bfloat16>::value) v += __bfloat162float(*dst);
+        else v += __half2float(*dst);
+      }
       if constexpr (sizeof(OutT) == 4) {
         *dst = v;
       } else if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
@@ -636,7 +672,7 @@ gemm_tn_pair_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const int col_base = n_blk * kWideBN + h * 256;
       const bool tile_fast = vec_ok && !p.masked && (row0 + 128 <= p.m_valid) && (col_base + 256 <= p.n_valid);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + h * 256;
-      if (tile_fast) {
+      if (tile_fast && !p.accumulate) {
 #pragma unroll 1
         for (int b = 0; b < 256 / kBoxCols; ++b) {
           uint32_t r[32], r2[32];
@@ -697,7 +733,7 @@ gemm_tn_pair_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           if (col_base + ch * 32 < p.n_valid) {
             int d = peers.first;
             for (int i = 0; i < peers.count; ++i) {
-              store_chunk<OutT>(static_cast<OutT*>(peers.ptr[d]), p, row, col_base + ch * 32, r, false);
+              store_chunk<OutT>(static_cast<OutT*>(peers.ptr[d]), p, row, col_base + ch * 32, r, tile_fast);
               if (++d == peers.count) d = 0;
             }
           }
@@ -841,6 +877,7 @@ int launch_typed(const CUtensorMap& ta, const CUtensorMap& tb, void* c, const Ge
   }
   gemm_tn_kernel<OutT><<<grid, kNumThreads, kSmemBytes, stream>>>(ta, tb, static_cast<OutT*>(c), gp, idesc, vec_ok, status);
   SILE_CUDA_TRY(cudaGetLastError());
+  note_kernel(sizeof(OutT) == 4 ? "gemm_tn_kernel<f32>" : "gemm_tn_kernel<16-bit>", grid, kNumThreads, kSmemBytes);
   return SILE_OK;
 }
 
@@ -922,6 +959,9 @@ int launch_pair_typed(const CUtensorMap& ta, const CUtensorMap& tb, void* c, con
   } else {
     SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, PairKernel<OutT, kWide>::fn(), ta, tb, static_cast<OutT*>(c), gp, idesc, vec_ok, status));
   }
+  note_kernel(kWide ? (sizeof(OutT) == 4 ? "gemm_tn_pair_wide_kernel<f32>" : "gemm_tn_pair_wide_kernel<16-bit>")
+                    : (sizeof(OutT) == 4 ? "gemm_tn_pair_kernel<f32>" : "gemm_tn_pair_kernel<16-bit>"),
+              cfg.gridDim.x, cfg.blockDim.x, cfg.dynamicSmemBytes);
   return SILE_OK;
 }
 
@@ -1004,6 +1044,8 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
   gp.ntg = p.num_threadgroups;
   gp.masked = p.num_threadgroups < total_logical ? 1 : 0;
   gp.group_m = raster_group_m();
+  gp.accumulate = p.accumulate ? 1 : 0;
+  if (p.accumulate && p.num_peers > 0) return fail(SILE_ERR_UNSUPPORTED, "matmul: a seeded accumulator cannot be combined with the fused all-gather");
 
   CUtensorMap ta, tb;
   const bool bf16 = p.in_dtype != SILE_DTYPE_F16;
@@ -1186,6 +1228,23 @@ int noalloc_setup(int dev, NoAllocDevice* out) {
 }
 
 }  // namespace
+
+int noalloc_read_and_clear_status(int* value) {
+  *value = 0;
+  int dev = 0;
+  SILE_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return SILE_OK;
+  int* word = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    word = g_noalloc_dev[dev].status;
+  }
+  if (!word) return SILE_OK;  // the entry point has not run on this device
+  SILE_CUDA_TRY(cudaMemcpy(value, word, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*value != 0) SILE_CUDA_TRY(cudaMemset(word, 0, sizeof(int)));
+  return SILE_OK;
+}
+
 }  // namespace sile
 
 extern "C" int sile_cuda_matmul_f32_noalloc(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
@@ -1278,11 +1337,8 @@ extern "C" int sile_cuda_matmul_f32_noalloc(const float* a, const float* b, floa
   if (wait) {
     SILE_CUDA_TRY(cudaStreamSynchronize(stream));
     int st = 0;
-    SILE_CUDA_TRY(cudaMemcpy(&st, nd.status, sizeof(int), cudaMemcpyDeviceToHost));
-    if (st != 0) {
-      SILE_CUDA_TRY(cudaMemset(nd.status, 0, sizeof(int)));
-      return fail(st & 0xff, "matmul_f32_noalloc: a device-side wait ran out (code %d); the result is invalid", st & 0xff);
-    }
+    if (int rc = noalloc_read_and_clear_status(&st)) return rc;
+    return decode_status_word(st);
   }
   return SILE_OK;
 }

@@ -25,6 +25,27 @@ int fail(int code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
 // Allocated on first use for the current device; never freed.
 int device_status_word(int** out);
 
+// Maps a status word as the kernels write it (low byte: SILE_ERR_* code; bit 8 + n: wait site n
+// was stuck) to the library's error: records the message and returns the code; 0 -> SILE_OK.
+int decode_status_word(int word);
+
+// The allocation-free matmul keeps its own status word inside the library image; this reads it
+// into *value and clears it if it is non-zero (0 if that entry point was never used on the
+// current device).
+int noalloc_read_and_clear_status(int* value);
+
+// A zero-initialisable work counter for one launch of a persistent kernel.  Counters come from a
+// per-device pool of 1024 handed out round-robin; the launch resets its counter in stream order,
+// so launches that overlap on different streams never share one unless more than 1024 launches
+// are in flight on the device at once.  Allocated on first use; never freed.
+int device_work_counter(int** out);
+
+// Records the kernel a launch chose and its geometry for sile_cuda_last_kernel(), and prints it
+// to stderr when SILE_PRINT_SOURCE, SILE_PRINT_LLVMIR or SILE_PRINT_TILEIR is set -- the
+// reference dumps its generated source / IR under those names
+// (crates/sile/src/kernel_launcher.rs:11-13,48-53); here the "source" is a hand-written kernel.
+void note_kernel(const char* name, unsigned grid, unsigned block, size_t smem_bytes);
+
 // cuTensorMapEncodeTiled through the runtime's driver entry-point lookup (no link
 // dependency on libcuda).  Strides are in bytes and exclude the innermost one.
 int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank, const void* base,
@@ -45,6 +66,8 @@ struct GemmProblem {
   // which part of C is written (whole tiles only, K remainder dropped), never the CTA tiling.
   int64_t bm = 1, bn = 1, bk = 1;
   int64_t num_threadgroups = INT64_MAX;
+  // D = C + A * B: the accumulator is seeded with what C holds (SILE_FLAG_ACCUMULATE).
+  bool accumulate = false;
   // Fused all-gather: when num_peers > 0 every output element is stored into each peer_c[i]
   // (same layout and leading dimension as c) instead of c; peer_first rotates the order.
   void* peer_c[8] = {nullptr};
@@ -88,8 +111,9 @@ struct AttnProblem {
   void* peer_o[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 int attention_launch(const AttnProblem& p, cudaStream_t stream);
-// CTA-pair kernel; arguments already validated by attention_launch.
+// CTA-pair kernel and persistent kernel; arguments already validated by attention_launch.
 int attention_pair_launch(const AttnProblem& p, cudaStream_t stream);
+int attention_persistent_launch(const AttnProblem& p, cudaStream_t stream);
 
 // ---- standalone tile ops (HBM-bound) --------------------------------------------
 int vec_add_launch(const float* a, const float* b, float* c, int64_t n, cudaStream_t stream);
@@ -98,5 +122,16 @@ int softmax_rows_launch(const float* x, int64_t ldx, float* y, int64_t ldy, int6
                         cudaStream_t stream);
 int reduce_sum_launch(const float* a, int64_t n, float* out, cudaStream_t stream);
 int matvec_launch(const float* x, const float* y, float* z, int64_t m, int64_t k, cudaStream_t stream);
+// f32 <-> bf16 conversions around the bf16 attention kernel (n elements, n % 8 == 0), and the
+// transposing one for K given as [BH][D][S] f32 -> [BH][S][D] bf16.
+int cast_f32_to_bf16_launch(const float* src, void* dst, int64_t n, cudaStream_t stream);
+int cast_bf16_to_f32_launch(const void* src, float* dst, int64_t n, cudaStream_t stream);
+int transpose_cast_kt_launch(const float* kt, void* k, int64_t bh, int64_t s, int64_t d, cudaStream_t stream);
+// Row softmax over column tiles: row r of tile column j (bn columns at x + r * ldx + j * bn) is
+// normalised on its own, as the reference does for a [BM, BN] tile narrower than the row
+// (crates/sile/examples/softmax.rs:3-16).  Only rows / tile columns whose logical tile id
+// (r / bm) * tiles_n + j is below num_tiles are written.
+int softmax_tiles_launch(const float* x, int64_t ldx, float* y, int64_t ldy, int64_t rows, int64_t tiles_n, int64_t bm,
+                         int64_t bn, int64_t num_tiles, cudaStream_t stream);
 
 }  // namespace sile

@@ -3,6 +3,8 @@
 // Each replaces one generated scalar loop nest of the reference's lowering
 // (crates/sile-tile-ir/src/passes/lowering/{tile_expr.rs,tile_compute/reduce.rs,
 // tile_compute/fused_reduce.rs,block_scalar.rs}).
+#include <cuda_bf16.h>
+
 #include <algorithm>
 
 #include "internal.h"
@@ -291,7 +293,94 @@ __global__ void unshard_columns_kernel(uint4* __restrict__ dst, const uint4* __r
 
 bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
+// ---- dtype / layout conversions around the bf16 attention kernel ---------------------------------
+// The reference's tensors are f32 and its DSL has no transpose, so an attention kernel composed
+// from its tile ops receives Q, V as [B*H*S, D] and K already transposed as [B*H*D, S]
+// (crates/sile-tile-ir/src/passes/lowering/tile_memory.rs:164-228: rank-2 row-major tiles only).
+// These kernels bring such buffers into the [B*H, S, D] bf16 layout the tensor-core kernel reads,
+// and its bf16 output back to f32.  HBM-bound: 16-byte accesses, 6 bytes per element.
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n8) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float4 a = __ldcs(reinterpret_cast<const float4*>(src) + 2 * i);
+    const float4 b = __ldcs(reinterpret_cast<const float4*>(src) + 2 * i + 1);
+    uint4 o;
+    __nv_bfloat162 t;
+    t = __floats2bfloat162_rn(a.x, a.y); o.x = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(a.z, a.w); o.y = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(b.x, b.y); o.z = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(b.z, b.w); o.w = *reinterpret_cast<uint32_t*>(&t);
+    reinterpret_cast<uint4*>(dst)[i] = o;
+  }
+}
+
+__global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, int64_t n8) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 v = reinterpret_cast<const uint4*>(src)[i];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float f[8];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      f[2 * h] = __uint_as_float(w[h] << 16);
+      f[2 * h + 1] = __uint_as_float(w[h] & 0xffff0000u);
+    }
+    __stcs(reinterpret_cast<float4*>(dst) + 2 * i, make_float4(f[0], f[1], f[2], f[3]));
+    __stcs(reinterpret_cast<float4*>(dst) + 2 * i + 1, make_float4(f[4], f[5], f[6], f[7]));
+  }
+}
+
+// kt [BH][D][S] f32 -> k [BH][S][D] bf16.  Block = 32 x 8 threads, tile = 64 (d) x 32 (s): reads run
+// along s, writes along d (two elements per thread, 128 bytes per warp).
+__global__ void transpose_cast_kt_kernel(const float* __restrict__ kt, __nv_bfloat16* __restrict__ k, int s, int d) {
+  __shared__ float tile[64][33];
+  const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 64;
+  const int64_t head = blockIdx.z;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const float* src = kt + head * static_cast<int64_t>(d) * s;
+  __nv_bfloat16* dst = k + head * static_cast<int64_t>(s) * d;
+#pragma unroll
+  for (int dd = ty; dd < 64; dd += 8) {
+    const int di = d0 + dd, si = s0 + tx;
+    tile[dd][tx] = (di < d && si < s) ? __ldcs(src + static_cast<int64_t>(di) * s + si) : 0.0f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int ss = ty; ss < 32; ss += 8) {
+    const int si = s0 + ss, di = d0 + 2 * tx;
+    if (si < s && di + 1 < d) {
+      const __nv_bfloat162 v = __floats2bfloat162_rn(tile[2 * tx][ss], tile[2 * tx + 1][ss]);
+      *reinterpret_cast<__nv_bfloat162*>(dst + static_cast<int64_t>(si) * d + di) = v;
+    }
+  }
+}
+
 }  // namespace
+
+int cast_f32_to_bf16_launch(const float* src, void* dst, int64_t n, cudaStream_t stream) {
+  if (n <= 0) return SILE_OK;
+  if (n % 8 != 0 || !aligned16(src) || !aligned16(dst)) return fail(SILE_ERR_UNSUPPORTED, "cast: element count must be a multiple of 8 and buffers 16-byte aligned");
+  cast_f32_to_bf16_kernel<<<grid_for(n / 8, 8), kThreads, 0, stream>>>(src, static_cast<__nv_bfloat16*>(dst), n / 8);
+  SILE_CUDA_TRY(cudaGetLastError());
+  return SILE_OK;
+}
+
+int cast_bf16_to_f32_launch(const void* src, float* dst, int64_t n, cudaStream_t stream) {
+  if (n <= 0) return SILE_OK;
+  if (n % 8 != 0 || !aligned16(src) || !aligned16(dst)) return fail(SILE_ERR_UNSUPPORTED, "cast: element count must be a multiple of 8 and buffers 16-byte aligned");
+  cast_bf16_to_f32_kernel<<<grid_for(n / 8, 8), kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), dst, n / 8);
+  SILE_CUDA_TRY(cudaGetLastError());
+  return SILE_OK;
+}
+
+int transpose_cast_kt_launch(const float* kt, void* k, int64_t bh, int64_t s, int64_t d, cudaStream_t stream) {
+  if (bh <= 0 || s <= 0 || d <= 0) return SILE_OK;
+  if (d % 2 != 0 || bh > 65535) return fail(SILE_ERR_UNSUPPORTED, "attention: head_dim must be even and batch*heads at most 65535 for f32 inputs");
+  dim3 grid(static_cast<unsigned>((s + 31) / 32), static_cast<unsigned>((d + 63) / 64), static_cast<unsigned>(bh));
+  transpose_cast_kt_kernel<<<grid, dim3(32, 8), 0, stream>>>(kt, static_cast<__nv_bfloat16*>(k), static_cast<int>(s), static_cast<int>(d));
+  SILE_CUDA_TRY(cudaGetLastError());
+  return SILE_OK;
+}
 
 int unshard_columns_launch(void* dst, const void* src, int64_t parts, int64_t rows, int64_t cols, int elt_size,
                            cudaStream_t stream) {

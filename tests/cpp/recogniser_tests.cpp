@@ -156,8 +156,21 @@ static bool desc_is(const SileKernelDesc& d, int op, std::vector<int64_t> consts
   return true;
 }
 
+// The matmul body with the accumulator seeded from the output tile: `D = acc + A * B`, the
+// reference's general mma (crates/sile-tile-ir/src/passes/lowering/tile_compute/mma.rs:25-260).
+static Kernel build_seeded_matmul_kernel(int64_t bm, int64_t bn, int64_t bk) {
+  Kernel k = build_dynamic_k_matmul_kernel(bm, bn, bk, false, "matmul_acc");
+  k.body[2] = Stmt::Let("acc", B(BuiltinOp::LoadTile, {Expr::Var("c"), syms({"BM", "BN"}), syms({"m_idx", "n_idx"})}));
+  return k;
+}
+
 // ---- recognition only ------------------------------------------------------------------------
 static void recognises_the_reference_examples() {
+  {
+    const SileKernelDesc d = recognise(build_seeded_matmul_kernel(2, 2, 2));
+    CHECK(desc_is(d, SILE_OP_MATMUL, {2, 2, 2}) && d.flags == SILE_FLAG_ACCUMULATE, "matmul with the accumulator seeded from c");
+    CHECK(recognise(build_dynamic_k_matmul_kernel(2, 2, 2, false)).flags == 0, "canonical matmul carries no flag");
+  }
   CHECK(desc_is(recognise(build_vec_add_kernel()), SILE_OP_VEC_ADD, {4}), "vec_add");
   CHECK(desc_is(recognise(build_dynamic_k_matmul_kernel(2, 2, 2, false)), SILE_OP_MATMUL, {2, 2, 2}), "matmul");
   CHECK(desc_is(recognise(build_dynamic_k_matmul_kernel(32, 16, 8, true, "gemm")), SILE_OP_MATMUL, {32, 16, 8}), "gemm with k_tiles alias");
@@ -202,6 +215,13 @@ static void refuses_near_misses() {
     k.body[2] = Stmt::Let("acc", B(BuiltinOp::Constant, {Expr::ScalarF32(1.0f), syms({"BM", "BN"})}));
     CHECK(refused(k), "non-zero accumulator");
   }
+  {  // accumulator seeded from the A operand's tensor, or from another tile of c
+    Kernel k = build_seeded_matmul_kernel(2, 2, 2);
+    k.body[2] = Stmt::Let("acc", B(BuiltinOp::LoadTile, {Expr::Var("a"), syms({"BM", "BN"}), syms({"m_idx", "n_idx"})}));
+    CHECK(refused(k), "accumulator seeded from a");
+    k.body[2] = Stmt::Let("acc", B(BuiltinOp::LoadTile, {Expr::Var("c"), syms({"BM", "BN"}), syms({"n_idx", "m_idx"})}));
+    CHECK(refused(k), "accumulator seeded from the transposed tile of c");
+  }
   {  // trip count over a.shape()[0]
     Kernel k = build_dynamic_k_matmul_kernel(2, 2, 2, false);
     k.body[3].expr = B(BuiltinOp::Div, {B(BuiltinOp::ShapeDim, {Expr::Var("a"), Expr::ScalarI64(0)}), Expr::ScalarI64(2)});
@@ -242,6 +262,33 @@ static void recognised_dynamic_k_matmul_runs() {
   const float expected[16] = {4, 6, 40, 30, 12, 14, 96, 70, 20, 22, 152, 110, 28, 30, 208, 150};
   const std::vector<float> actual = c.to_vec(stream);
   for (int i = 0; i < 16; ++i) CHECK(std::fabs(actual[i] - expected[i]) < 1e-4f, "mismatch at %d: got %f, expected %f", i, actual[i], expected[i]);
+}
+
+// The inputs of llvm_ir_cpu_runtime.rs:44-103 with c holding 100 + index before the launch: the
+// general mma starts every sum from the accumulator's value, so each output is that seed plus the
+// reference test's expected product.
+static void recognised_seeded_matmul_runs() {
+  Device device = Device::cuda();
+  auto stream = device.create_stream();
+  Tensor a = Tensor::from_vec({1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16}, {4, 4}, device);
+  Tensor b = Tensor::from_vec({1, 0, 2, 1, 0, 1, 3, 2, 1, 0, 4, 3, 0, 1, 5, 4}, {4, 4}, device);
+  std::vector<float> seed(16);
+  for (int i = 0; i < 16; ++i) seed[i] = 100.0f + static_cast<float>(i);
+  Tensor c = Tensor::from_vec(seed, {4, 4}, device);
+  launcher_for(build_seeded_matmul_kernel(2, 2, 2), args_of({&a, &b, &c})).grid({4, 1, 1}).apply(stream);
+  const float product[16] = {4, 6, 40, 30, 12, 14, 96, 70, 20, 22, 152, 110, 28, 30, 208, 150};
+  const std::vector<float> actual = c.to_vec(stream);
+  for (int i = 0; i < 16; ++i)
+    CHECK(std::fabs(actual[i] - (seed[i] + product[i])) < 1e-4f, "mismatch at %d: got %f, expected %f", i, actual[i], seed[i] + product[i]);
+  // a short grid leaves the tiles past it with their seed
+  Tensor c2 = Tensor::from_vec(seed, {4, 4}, device);
+  launcher_for(build_seeded_matmul_kernel(2, 2, 2), args_of({&a, &b, &c2})).grid({3, 1, 1}).apply(stream);
+  const std::vector<float> part = c2.to_vec(stream);
+  for (int i = 0; i < 16; ++i) {
+    const bool last_tile = (i / 4) >= 2 && (i % 4) >= 2;
+    const float want = last_tile ? seed[i] : seed[i] + product[i];
+    CHECK(std::fabs(part[i] - want) < 1e-4f, "short grid, element %d: got %f, expected %f", i, part[i], want);
+  }
 }
 
 // llvm_ir_cpu_runtime.rs:8-42 and 105-141
@@ -311,6 +358,7 @@ int main(int argc, char** argv) {
       {"names_do_not_matter_structure_does", names_do_not_matter_structure_does, false},
       {"refuses_near_misses", refuses_near_misses, false},
       {"recognised_dynamic_k_matmul_runs", recognised_dynamic_k_matmul_runs, true},
+      {"recognised_seeded_matmul_runs", recognised_seeded_matmul_runs, true},
       {"recognised_vec_add_and_relu_run", recognised_vec_add_and_relu_run, true},
       {"recognised_softmax_reduce_and_mlp_run", recognised_softmax_reduce_and_mlp_run, true},
   };

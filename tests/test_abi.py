@@ -35,6 +35,19 @@ def test_version_and_error_string(lib):
     assert isinstance(lib.sile_cuda_last_error(), bytes)
 
 
+def test_status_word_maps_to_timeout_error(lib):
+    """The word a kernel leaves after a bounded wait ran out -> code and message, as the blocking
+    entry points report it after reading the word back (host-side mapping only: no GPU wait is
+    made to run out here)."""
+    import sile_b200
+    assert lib.sile_cuda_decode_status(0) == sile_b200._lib.OK
+    word = sile_b200._lib.ERR_TIMEOUT | (1 << (8 + 3)) | (1 << (8 + 8))
+    assert lib.sile_cuda_decode_status(word) == sile_b200._lib.ERR_TIMEOUT
+    msg = lib.sile_cuda_last_error()
+    assert b"wait ran out" in msg and b"0x108" in msg
+    assert lib.sile_cuda_last_status() == sile_b200._lib.ERR_TIMEOUT
+
+
 def test_bind_consts_validation(lib):
     import ctypes as C
     import sile_b200

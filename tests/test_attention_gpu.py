@@ -20,9 +20,10 @@ def sb():
     return sile_b200
 
 
-@pytest.fixture(params=["single", "pair"], autouse=True)
+@pytest.fixture(params=["single", "persistent", "pair"], autouse=True)
 def attn_kernel(request, monkeypatch):
-    """Every case runs on both kernels: the one-CTA default and the CTA-pair (cta_group::2) one."""
+    """Every case runs on all three kernels: the one-CTA-per-item default, the persistent kernel
+    and the CTA-pair (cta_group::2) one."""
     monkeypatch.setenv("SILE_CUDA_ATTN_KERNEL", request.param)
     return request.param
 
@@ -156,10 +157,10 @@ def test_a5_causal_shard_h32_s8192_sampled(sb, oracle):
 def test_fused_allgather_epilogue_on_one_gpu(sb, attn_kernel, causal):
     """sile_cuda_attention_allgather with the ranks played in turn on one GPU: every "rank" owns a
     slab of heads and stores it into all destination buffers; afterwards each buffer must equal
-    the unsharded result.  (The entry point always runs the one-CTA kernel.)"""
+    the unsharded result."""
     import torch
-    if attn_kernel != "single":
-        pytest.skip("one pass is enough: the entry point does not depend on the kernel variant")
+    if attn_kernel == "pair":
+        pytest.skip("the entry point runs the persistent or the one-CTA-per-item kernel only")
     world, bh_local, s = 4, 3, 700
     q, k, v = _inputs(world * bh_local, s, 128, 21)
     want = torch.zeros_like(q)

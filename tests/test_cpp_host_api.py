@@ -63,4 +63,4 @@ def test_recognised_kernels_on_the_cuda_device(recogniser_binary):
         pytest.skip("no CUDA device")
     r = subprocess.run([recogniser_binary], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
-    assert "6 cases, 0 failures" in r.stdout
+    assert "7 cases, 0 failures" in r.stdout
