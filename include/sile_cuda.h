@@ -50,7 +50,10 @@ extern "C" {
  * one generated unit of the reference (canonical_matmul.rs:24-444 and the per-op
  * loop nests of crates/sile-tile-ir/src/passes/lowering/). */
 #define SILE_OP_MATMUL 1          /* examples/matmul.rs:3-18 */
-#define SILE_OP_ATTENTION 2       /* composed from mma/reduce_max/exp/reduce_sum tile ops */
+#define SILE_OP_ATTENTION 2       /* composed from mma/reduce_max/exp/reduce_sum tile ops.  Two forms:
+                                     16-bit q, k, v, o of one shape [.., S, 128] (rank 2..4); or, with
+                                     in/out dtype F32, the reference's rank-2 tensors with K transposed
+                                     (see sile_kernel_attention) */
 #define SILE_OP_VEC_ADD 3         /* examples/vec_add.rs:3-10 */
 #define SILE_OP_RELU 4            /* examples/mlp.rs:51-55 */
 #define SILE_OP_SOFTMAX 5         /* examples/softmax.rs:3-16 */
@@ -78,7 +81,8 @@ typedef struct SileKernelDesc {
   float scale;          /* attention: softmax scale applied to Q*K^T */
   int32_t flags;        /* SILE_FLAG_* bits; 0 for the kernels of the reference's examples */
   int64_t consts[4];    /* matmul: BM,BN,BK; vec_add/parallel_reduce: TILE;
-                           softmax: BM,BN; matvec: BM,BK; 0 = unspecified (treated as 1) */
+                           softmax: BM,BN; matvec: BM,BK; attention over f32 tensors: BM,BN;
+                           0 = unspecified (treated as 1) */
 } SileKernelDesc;
 
 /* ---- 1. exact reference ABI -------------------------------------------------
@@ -106,12 +110,33 @@ void sile_kernel_parallel_reduce(void** buffers, int64_t num_threadgroups, int64
                                  const int64_t* shapes, int64_t num_shapes);
 void sile_kernel_matvec(void** buffers, int64_t num_threadgroups, int64_t threads_per_group,
                         const int64_t* shapes, int64_t num_shapes);
+/* Attention forward as the reference's tile ops compose it (load_tile, mma, reduce_max, max_tile,
+ * exp, reduce_sum, broadcast, div: crates/sile-tile-ir/src/lower.rs:509-748; general mma
+ * crates/sile-tile-ir/src/passes/lowering/tile_compute/mma.rs:25-260), over the reference's tensor
+ * model -- f32, rank 2, row-major (crates/sile-hir/src/types.rs:11-14) -- with K given TRANSPOSED
+ * because `mma` takes [BM,K] x [K,BN] tiles and the DSL has no transpose op:
+ *   buffers = q [BH*S, D], kt [BH*D, S], v [BH*S, D], o [BH*S, D];  shapes = those eight extents.
+ * One logical tile = BM query rows of one head; tiles [0, grid product) run
+ * (crates/sile-backend/src/cpu/codegen.rs:517-533), the rest of o is left untouched.  Const
+ * generics bound under the name "attention": BM, BN, causal (0/1; a surface extension, the DSL
+ * has no index tile to build a mask from); the softmax scale, a literal in the kernel body, is
+ * bound with sile_cuda_bind_scale.  D must be 128; S must be a multiple of BM and of BN (a query
+ * tile may not straddle heads, and the composed kernel's key loop would drop a BN remainder).
+ * The tensor cores run in bf16 with f32 accumulation: q, kt, v are rounded to bf16 on the
+ * device, so results carry the 2e-2 tolerance of the 16-bit configurations, not 1e-3. */
+void sile_kernel_attention(void** buffers, int64_t num_threadgroups, int64_t threads_per_group,
+                           const int64_t* shapes, int64_t num_shapes);
 
 /* The reference bakes const generics (tile sizes) into each generated kernel
  * (crates/sile-tile-ir/src/lower.rs:9-34); the exact ABI has no slot for them.
  * This binds them for subsequent sile_kernel_<name> calls from the calling
  * thread.  `name` is the kernel name without the "sile_kernel_" prefix. */
 int sile_cuda_bind_consts(const char* name, const int64_t* consts, int64_t num_consts);
+
+/* A float literal of a kernel body that the exact ABI has no slot for either: the softmax scale
+ * of "attention" (a constant tile in the reference's DSL, crates/sile-tile-ir/src/lower.rs:509-524).
+ * Bound per calling thread like the const generics. */
+int sile_cuda_bind_scale(const char* name, float scale);
 
 /* ---- 2. Device::Cuda launch ---------------------------------------------------
  * The arm crates/sile/src/kernel_launcher.rs:69-71 leaves unimplemented, shaped

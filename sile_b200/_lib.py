@@ -17,7 +17,7 @@ OP_MATMUL, OP_ATTENTION, OP_VEC_ADD, OP_RELU, OP_SOFTMAX, OP_PARALLEL_REDUCE, OP
 # Every symbol include/sile_cuda.h declares.
 EXPORTED_SYMBOLS = (
     "sile_kernel_matmul", "sile_kernel_matmul_acc", "sile_kernel_vec_add", "sile_kernel_relu", "sile_kernel_softmax",
-    "sile_kernel_parallel_reduce", "sile_kernel_matvec", "sile_cuda_bind_consts",
+    "sile_kernel_parallel_reduce", "sile_kernel_matvec", "sile_kernel_attention", "sile_cuda_bind_consts", "sile_cuda_bind_scale",
     "sile_cuda_launch", "sile_cuda_launch_host", "sile_cuda_matmul_shard",
     "sile_cuda_matmul_allgather", "sile_cuda_attention_allgather", "sile_cuda_unshard_columns", "sile_cuda_matmul_f32_noalloc", "sile_cuda_set_device",
     "sile_cuda_device_count", "sile_cuda_synchronize", "sile_cuda_decode_status", "sile_cuda_malloc", "sile_cuda_free",
@@ -56,6 +56,7 @@ def lib() -> C.CDLL:
             fn = getattr(L, name)
             fn.argtypes, fn.restype = ksig, None
     L.sile_cuda_bind_consts.argtypes = [C.c_char_p, C.POINTER(_i64), _i64]
+    L.sile_cuda_bind_scale.argtypes = [C.c_char_p, C.c_float]
     L.sile_cuda_launch.argtypes = [C.POINTER(KernelDesc), C.POINTER(C.c_void_p), C.POINTER(_i64), _i64,
                                    C.POINTER(C.c_uint32), C.c_void_p]
     L.sile_cuda_launch_host.argtypes = [C.POINTER(KernelDesc), C.POINTER(C.c_void_p), C.POINTER(_i64), _i64,

@@ -117,6 +117,18 @@ def attention(q, k, v, o, scale: float, causal: bool = False) -> KernelLauncher:
     return KernelLauncher(desc, [q, k, v, o]).grid((q.numel() // (q.shape[-1] * q.shape[-2]), 1, 1))
 
 
+def attention_f32(q, kt, v, o, bm: int, bn: int, scale: float, causal: bool = False) -> KernelLauncher:
+    """Attention over the reference's own tensor model: f32 rank-2 ``q [BH*S, D]``, ``kt [BH*D, S]``
+    (K transposed: the DSL's ``mma`` takes [BM,K] x [K,BN] tiles and has no transpose), ``v``, ``o``
+    ``[BH*S, D]``; one logical tile = ``bm`` query rows.  Device or host buffers."""
+    desc = make_desc(OP_ATTENTION, DTYPE_F32, DTYPE_F32, causal=causal, scale=scale, consts=(bm, bn))
+    return KernelLauncher(desc, [q, kt, v, o]).grid((q.shape[0] // bm, 1, 1))
+
+
+def bind_scale(name: str, scale: float) -> None:
+    _check(_lib.lib().sile_cuda_bind_scale(name.encode(), C.c_float(scale)))
+
+
 def vec_add(a, b, c, tile=4) -> KernelLauncher:
     return KernelLauncher(make_desc(OP_VEC_ADD, consts=(tile,)), [a, b, c]).grid((a.shape[0] // tile, 1, 1))
 
@@ -125,8 +137,11 @@ def relu(x) -> KernelLauncher:
     return KernelLauncher(make_desc(OP_RELU), [x]).grid((1, 1, 1))
 
 
-def softmax(x, y, bm=1) -> KernelLauncher:
-    return KernelLauncher(make_desc(OP_SOFTMAX, consts=(bm, x.shape[1])), [x, y]).grid((x.shape[0] // bm, 1, 1))
+def softmax(x, y, bm=1, bn=None) -> KernelLauncher:
+    """``softmax::<BM,BN>(&x, &mut y)`` (crates/sile/examples/softmax.rs:3-16): every [bm, bn] tile is
+    normalised on its own; ``bn`` defaults to the whole row."""
+    bn = x.shape[1] if bn is None else bn
+    return KernelLauncher(make_desc(OP_SOFTMAX, consts=(bm, bn)), [x, y]).grid((x.shape[0] // bm, max(x.shape[1] // bn, 1), 1))
 
 
 def parallel_reduce(a, out, tile=1) -> KernelLauncher:

@@ -24,6 +24,8 @@ struct BoundConsts {
   int64_t softmax[2] = {1, 0};  // BN = 0: whole row
   int64_t parallel_reduce[1] = {1};
   int64_t matvec[2] = {1, 1};
+  int64_t attention[3] = {1, 1, 0};  // BM, BN, causal
+  float attention_scale = 1.0f;
 };
 thread_local BoundConsts t_consts;
 
@@ -193,6 +195,34 @@ struct ArgSpan {
   bool is_output;
 };
 
+// Attention over the reference's f32 rank-2 tensors: shapes q [BH*S, D], kt [BH*D, S], v, o [BH*S, D].
+struct AttnF32Dims {
+  int64_t bh, s, d, rows, rows_written;
+};
+int attention_f32_dims(const SileKernelDesc* d, const int64_t* shapes, int64_t ns, int64_t ntg, AttnF32Dims* out) {
+  if (ns != 8) return fail(SILE_ERR_INVALID, "attention (f32): expected q[BH*S,D] kt[BH*D,S] v[BH*S,D] o[BH*S,D]");
+  const int64_t rows = shapes[0], dd = shapes[1], s = shapes[3];
+  if (rows <= 0 || dd <= 0 || s <= 0) return fail(SILE_ERR_INVALID, "attention: non-positive dimension");
+  if (rows % s != 0 || shapes[2] != rows / s * dd || shapes[4] != rows || shapes[5] != dd || shapes[6] != rows || shapes[7] != dd)
+    return fail(SILE_ERR_INVALID, "attention (f32): inconsistent shapes q[%lld,%lld] kt[%lld,%lld] v[%lld,%lld] o[%lld,%lld]",
+                (long long)shapes[0], (long long)shapes[1], (long long)shapes[2], (long long)shapes[3], (long long)shapes[4],
+                (long long)shapes[5], (long long)shapes[6], (long long)shapes[7]);
+  if (d->out_dtype != SILE_DTYPE_F32) return fail(SILE_ERR_UNSUPPORTED, "attention: f32 inputs give an f32 output");
+  // [BM, D] query tiles and [D, BN] key tiles of the flattened tensors: a query tile must not
+  // straddle two heads, and keys past the last whole BN tile would be dropped by the composed
+  // kernel's loop (as the matmul's K remainder is) -- refused rather than silently different.
+  const int64_t bm = d->consts[0] > 0 ? d->consts[0] : 1, bn = d->consts[1] > 0 ? d->consts[1] : 1;
+  if (s % bm != 0 || s % bn != 0)
+    return fail(SILE_ERR_UNSUPPORTED, "attention (f32): sequence length %lld must be a multiple of BM = %lld and BN = %lld", (long long)s,
+                (long long)bm, (long long)bn);
+  out->bh = rows / s;
+  out->s = s;
+  out->d = dd;
+  out->rows = rows;
+  out->rows_written = std::min<int64_t>(ntg < 0 ? 0 : ntg, rows / bm) * bm;  // q tiles [0, grid) run (cpu/codegen.rs:517-533)
+  return SILE_OK;
+}
+
 // Validates shapes for `desc` and lists the byte size / direction of every buffer.
 int describe_args(const SileKernelDesc* d, const int64_t* shapes, int64_t ns, int64_t ntg, std::vector<ArgSpan>* out) {
   out->clear();
@@ -217,6 +247,18 @@ int describe_args(const SileKernelDesc* d, const int64_t* shapes, int64_t ns, in
       return SILE_OK;
     }
     case SILE_OP_ATTENTION: {
+      if (d->in_dtype == SILE_DTYPE_F32) {
+        // The reference's own tensor model: f32, rank 2, K given transposed (its DSL has no
+        // transpose op): q [BH*S, D], kt [BH*D, S], v [BH*S, D], o [BH*S, D].
+        AttnF32Dims a;
+        if (int rc = attention_f32_dims(d, shapes, ns, ntg, &a)) return rc;
+        const size_t bytes = static_cast<size_t>(a.rows) * a.d * 4;
+        out->push_back({bytes, true, false});
+        out->push_back({bytes, true, false});
+        out->push_back({bytes, true, false});
+        out->push_back({bytes, a.rows_written < a.rows, true});  // untouched rows must survive the round trip
+        return SILE_OK;
+      }
       if (ns % 4 != 0 || ns / 4 < 2 || ns / 4 > 4) return fail(SILE_ERR_INVALID, "attention: expected 4 buffers of rank 2..4");
       const int64_t r = ns / 4;
       int64_t elems = 1;
@@ -298,6 +340,35 @@ int launch_device(const SileKernelDesc* d, void* const* buf, const int64_t* shap
       return rc;
     }
     case SILE_OP_ATTENTION: {
+      if (d->in_dtype == SILE_DTYPE_F32) {
+        // f32 rank-2 tensors with K transposed: convert to the [BH, S, D] bf16 layout of the
+        // tensor-core kernel in scratch, run it on the heads the grid reaches, convert O back.
+        AttnF32Dims a;
+        if (int rc = attention_f32_dims(d, shapes, ns, ntg, &a)) return rc;
+        if (a.rows_written == 0) return SILE_OK;
+        const int64_t heads = (a.rows_written + a.s - 1) / a.s;
+        const size_t plane = static_cast<size_t>(heads) * a.s * a.d * 2;
+        void* ws = nullptr;
+        if (int rc = pool_alloc(&ws, 4 * plane, stream)) return rc;
+        char* qb = static_cast<char*>(ws);
+        char *kb = qb + plane, *vb = kb + plane, *ob = vb + plane;
+        const int64_t n = heads * a.s * a.d;
+        int rc = cast_f32_to_bf16_launch(static_cast<const float*>(buf[0]), qb, n, stream);
+        if (rc == SILE_OK) rc = transpose_cast_kt_launch(static_cast<const float*>(buf[1]), kb, heads, a.s, a.d, stream);
+        if (rc == SILE_OK) rc = cast_f32_to_bf16_launch(static_cast<const float*>(buf[2]), vb, n, stream);
+        if (rc == SILE_OK) {
+          AttnProblem p;
+          p.q = qb; p.k = kb; p.v = vb; p.o = ob;
+          p.bh = heads; p.s = a.s; p.d = a.d;
+          p.scale = d->scale;
+          p.causal = d->causal;
+          rc = attention_launch(p, stream);
+        }
+        if (rc == SILE_OK) rc = cast_bf16_to_f32_launch(ob, static_cast<float*>(buf[3]), a.rows_written * a.d, stream);
+        cudaError_t e = cudaFreeAsync(ws, stream);
+        if (rc == SILE_OK && e != cudaSuccess) return fail(SILE_ERR_CUDA, "cudaFreeAsync failed: %s", cudaGetErrorString(e));
+        return rc;
+      }
       const int64_t r = ns / 4;
       AttnProblem p;
       p.q = buf[0]; p.k = buf[1]; p.v = buf[2]; p.o = buf[3];
@@ -328,7 +399,15 @@ int launch_device(const SileKernelDesc* d, void* const* buf, const int64_t* shap
       const int64_t rows = shapes[2], cols = shapes[3];
       const int64_t bm = const_or_one(d, 0);
       const int64_t bn = d->consts[1] > 0 ? d->consts[1] : cols;
-      if (bn != cols) return fail(SILE_ERR_UNSUPPORTED, "softmax: BN (%lld) must span the row (%lld columns)", (long long)bn, (long long)cols);
+      if (bn > cols) return SILE_OK;  // no whole tile fits the row: nothing is launched
+      if (bn != cols) {
+        // BN narrower than the row: every [BM, BN] tile is a softmax of its own, as in the
+        // reference (examples/softmax.rs:3-16); columns past the last whole tile stay untouched
+        const int64_t tiles_n = cols / bn;
+        const int64_t num_tiles = std::min<int64_t>(ntg, (rows / bm) * tiles_n);
+        return softmax_tiles_launch(static_cast<const float*>(buf[0]), shapes[1], static_cast<float*>(buf[1]), cols, rows / bm * bm,
+                                    tiles_n, bm, bn, num_tiles, stream);
+      }
       const int64_t r = std::min<int64_t>(rows / bm, ntg) * bm;
       return softmax_rows_launch(static_cast<const float*>(buf[0]), shapes[1], static_cast<float*>(buf[1]), cols, r, cols, stream);
     }
@@ -660,7 +739,23 @@ int sile_cuda_bind_consts(const char* name, const int64_t* consts, int64_t n) {
   if (!std::strcmp(name, "softmax")) return set(t_consts.softmax, 2);
   if (!std::strcmp(name, "parallel_reduce")) return set(t_consts.parallel_reduce, 1);
   if (!std::strcmp(name, "matvec")) return set(t_consts.matvec, 2);
+  if (!std::strcmp(name, "attention")) {
+    // BM, BN and the causal flag (0 / 1), which is not a tile size and may be zero
+    if (n != 3) return fail(SILE_ERR_INVALID, "attention takes 3 const generics (BM, BN, causal), got %lld", (long long)n);
+    if (consts[0] <= 0 || consts[1] <= 0 || (consts[2] != 0 && consts[2] != 1))
+      return fail(SILE_ERR_INVALID, "attention: BM and BN must be positive and causal 0 or 1");
+    for (int i = 0; i < 3; ++i) t_consts.attention[i] = consts[i];
+    return SILE_OK;
+  }
   return fail(SILE_ERR_UNSUPPORTED, "no kernel named %s", name);
+}
+
+int sile_cuda_bind_scale(const char* name, float scale) {
+  if (!name) return fail(SILE_ERR_INVALID, "null argument");
+  if (std::strcmp(name, "attention") != 0) return fail(SILE_ERR_UNSUPPORTED, "kernel %s has no scale literal", name);
+  if (!(scale > 0.0f)) return fail(SILE_ERR_INVALID, "attention: scale must be positive");
+  t_consts.attention_scale = scale;
+  return SILE_OK;
 }
 
 int sile_cuda_launch(const SileKernelDesc* desc, void* const* dev_buffers, const int64_t* shapes, int64_t num_shapes,
@@ -793,6 +888,14 @@ void sile_kernel_softmax(void** buffers, int64_t num_threadgroups, int64_t threa
 void sile_kernel_parallel_reduce(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {
   SileKernelDesc d = f32_desc(SILE_OP_PARALLEL_REDUCE);
   d.consts[0] = t_consts.parallel_reduce[0];
+  launch_host(&d, buffers, shapes, num_shapes, num_threadgroups * threads_per_group);
+}
+void sile_kernel_attention(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {
+  SileKernelDesc d = f32_desc(SILE_OP_ATTENTION);
+  d.consts[0] = t_consts.attention[0];
+  d.consts[1] = t_consts.attention[1];
+  d.causal = static_cast<int32_t>(t_consts.attention[2]);
+  d.scale = t_consts.attention_scale;
   launch_host(&d, buffers, shapes, num_shapes, num_threadgroups * threads_per_group);
 }
 void sile_kernel_matvec(void** buffers, int64_t num_threadgroups, int64_t threads_per_group, const int64_t* shapes, int64_t num_shapes) {

@@ -126,6 +126,33 @@ __global__ void softmax_rows_kernel(const float* __restrict__ x, int64_t ldx, fl
   }
 }
 
+// Tile-local softmax: the reference normalises each [BM, BN] tile on its own
+// (examples/softmax.rs:3-16), so with BN smaller than the row every BN-wide segment of a row is a
+// softmax of its own.  One warp per (row, tile column) segment; a segment is written only if its
+// logical tile (row / bm) * tiles_n + tile column was launched (cpu/codegen.rs:517-533).
+__global__ void softmax_tiles_kernel(const float* __restrict__ x, int64_t ldx, float* __restrict__ y, int64_t ldy, int64_t rows,
+                                     int tiles_n, int bm, int bn, int64_t num_tiles) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int64_t warp_global = blockIdx.x * static_cast<int64_t>(warps_per_block) + (threadIdx.x >> 5);
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps_per_block;
+  const int64_t segments = rows * tiles_n;
+  for (int64_t seg = warp_global; seg < segments; seg += nwarps) {
+    const int64_t r = seg / tiles_n;
+    const int jt = static_cast<int>(seg - r * tiles_n);
+    if ((r / bm) * tiles_n + jt >= num_tiles) continue;
+    const float* xr = x + r * ldx + static_cast<int64_t>(jt) * bn;
+    float* yr = y + r * ldy + static_cast<int64_t>(jt) * bn;
+    float mx = -INFINITY;
+    for (int c = lane; c < bn; c += 32) mx = fmaxf(mx, xr[c]);
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    for (int c = lane; c < bn; c += 32) sum += expf(xr[c] - mx);
+    sum = warp_sum(sum);
+    for (int c = lane; c < bn; c += 32) yr[c] = expf(xr[c] - mx) / sum;
+  }
+}
+
 // Rows of up to 128 * kChunks columns with 16-byte aligned rows: each lane holds kChunks float4
 // (the row is read once, 512 bytes per warp load), all loads of a row are issued before the first
 // use, exp is ex2.approx on (x - max) * log2(e) and the division becomes one reciprocal per row.
@@ -424,6 +451,16 @@ int softmax_rows_launch(const float* x, int64_t ldx, float* y, int64_t ldy, int6
   } else {
     softmax_rows_kernel<<<grid_for(rows * 32, 8), kThreads, 0, stream>>>(x, ldx, y, ldy, rows, static_cast<int>(cols));
   }
+  SILE_CUDA_TRY(cudaGetLastError());
+  return SILE_OK;
+}
+
+int softmax_tiles_launch(const float* x, int64_t ldx, float* y, int64_t ldy, int64_t rows, int64_t tiles_n, int64_t bm, int64_t bn,
+                         int64_t num_tiles, cudaStream_t stream) {
+  if (rows <= 0 || tiles_n <= 0 || num_tiles <= 0) return SILE_OK;
+  if (bn > (1ll << 30) || tiles_n > (1ll << 30) || bm > (1ll << 30)) return fail(SILE_ERR_INVALID, "softmax: tile too large");
+  softmax_tiles_kernel<<<grid_for(rows * tiles_n * 32, 8), kThreads, 0, stream>>>(x, ldx, y, ldy, rows, static_cast<int>(tiles_n),
+                                                                                 static_cast<int>(bm), static_cast<int>(bn), num_tiles);
   SILE_CUDA_TRY(cudaGetLastError());
   return SILE_OK;
 }

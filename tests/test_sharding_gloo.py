@@ -43,6 +43,20 @@ def _worker(rank, world, port, q):
                 flat[idx.reshape(-1)] = g[j].reshape(-1)
         ok_mm = np.allclose(c, a @ b_colmajor.T, atol=1e-4)
 
+        # host-buffer path: each rank stages its row slab of A only, the slabs are all-gathered
+        hm = sharding.HostShardedMatmul(
+            m, n, k, world, rank, torch.float32,
+            compute=lambda af, bs, cs: cs.copy_(af @ bs.T),
+            device_empty=lambda shape, dt: torch.full(shape, float("nan"), dtype=dt),
+            all_gather=lambda full, part: dist.all_gather_into_tensor(full, part.clone()))
+        a_host = torch.from_numpy(a).clone()
+        a_host[:hm.r0] = float("nan")            # rows of other ranks' slabs must never be read here
+        a_host[hm.r0 + hm.rows:] = float("nan")
+        c_host = torch.zeros(m, nc)
+        hm.step(a_host, torch.from_numpy(np.ascontiguousarray(b_shard)), c_host)
+        ok_mm = ok_mm and np.allclose(c_host.numpy(), a @ b_shard.T, atol=1e-4)
+        ok_mm = ok_mm and hm.h2d_bytes == (m // world * k + nc * k) * 4
+
         bh, s, d = 6, 8, 4
         o_full = rng.standard_normal((bh, s, d)).astype(np.float32)    # stands for the attention output
         h0, hc = sharding.head_slab(bh, world, rank)

@@ -78,6 +78,29 @@ def test_softmax_matches_oracle(sb, oracle, rows, cols):
     assert np.abs(y.sum(axis=1) - 1.0).max() < 1e-4
 
 
+@pytest.mark.parametrize("rows,cols,bm,bn,short", [
+    (4, 8, 2, 4, 0),        # the reference example's tensor with half-row tiles
+    (64, 96, 8, 32, 0),
+    (33, 100, 4, 24, 0),    # rows and columns past the last whole tile stay untouched
+    (40, 1024, 5, 128, 7),  # a short grid stops in the middle of a tile row
+    (6, 4096, 3, 2048, 1),  # tiles longer than the register-cached row kernels handle
+])
+def test_tile_local_softmax_matches_oracle(sb, oracle, rows, cols, bm, bn, short):
+    """BN narrower than the row: every [BM, BN] tile is normalised on its own, as the reference's
+    kernel does (crates/sile/examples/softmax.rs:3-16)."""
+    x = uniform((rows, cols), 17) * 6
+    y = np.full_like(x, -3.0)
+    want = np.full_like(x, -3.0)
+    ntg = (rows // bm) * (cols // bn) - short
+    sb.bind_consts("softmax", (bm, bn))
+    sb.kernel_call("softmax", [x, y], grid=(ntg, 1, 1))
+    oracle.lib.sile_oracle_bind_softmax(bm, bn)
+    oracle.launch("softmax", [x, want], grid=(ntg, 1, 1))
+    untouched = want == -3.0
+    assert (y[untouched] == -3.0).all()
+    assert np.abs(y - want)[~untouched].max() < 1e-3 * want[~untouched].max()
+
+
 def test_parallel_reduce_golden(sb):
     # crates/sile/tests/backend_parallel_reduce.rs:16-28
     a = np.ones(100_000, np.float32)

@@ -56,6 +56,43 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point(sb):
         assert rel_err(got[:mv, :nv], a[:mv, :k // bk * bk].astype(np.float64) @ b[:k // bk * bk, :nv]) < F32_TOL
 
 
+def test_no_device_memory_is_allocated_and_k_below_bk(sb):
+    """What the entry point exists for: after its first call on the device, further calls of any
+    admissible size change neither the free memory the driver reports nor what the default
+    stream-ordered pool has reserved.  One of the sizes has K < BK: no k step runs, the planes are
+    all zero padding and every whole logical tile of C becomes 0.0, as with the allocating path."""
+    import torch
+    a, b = uniform((128, 64), 3), uniform((64, 128), 4)
+    warm = torch.zeros(128, 128, device="cuda")
+    assert _noalloc(sb, torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda(), warm, 1, 1, 1) == 0
+    cases = [(640, 512, 384, (64, 64, 32)), (96, 200, 24, (32, 40, 32)), (1000, 1000, 1000, (8, 8, 8))]
+    inputs = []
+    for m, n, k, tile in cases:
+        da, db = torch.from_numpy(uniform((m, k), m)).cuda(), torch.from_numpy(uniform((k, n), n)).cuda()
+        inputs.append((da, db, torch.full((m, n), -7.0, device="cuda"), torch.full((m, n), -7.0, device="cuda"), tile))
+    torch.cuda.synchronize()
+    pool = torch.cuda.memory.memory_stats()  # torch's own allocator must not move either
+    free_before = torch.cuda.mem_get_info()[0]
+    reserved_before = torch.cuda.memory_reserved()
+    for da, db, got, _, (bm, bn, bk) in inputs:
+        assert _noalloc(sb, da, db, got, bm, bn, bk) == 0, sb._lib.lib().sile_cuda_last_error()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_reserved() == reserved_before
+    del pool
+    for da, db, got, want, (bm, bn, bk) in inputs:
+        sb.matmul(da, db, want, bm, bn, bk).apply()
+        sb.synchronize()
+        m, n = got.shape
+        mv, nv = m // bm * bm, n // bn * bn
+        g, w = got.cpu().numpy(), want.cpu().numpy()
+        assert (g[mv:] == -7.0).all() and (g[:, nv:] == -7.0).all()
+        scale = max(np.abs(w[:mv, :nv]).max(), 1.0)
+        assert np.abs(g[:mv, :nv] - w[:mv, :nv]).max() < F32_TOL * scale
+    # K = 24 < BK = 32: zero k steps, whole logical tiles become exactly 0.0
+    assert (inputs[1][2].cpu().numpy()[:96, :200] == 0.0).all()
+
+
 def test_asynchronous_form_and_size_limit(sb):
     import torch
     a, b = uniform((256, 512), 1), uniform((512, 384), 2)
