@@ -344,7 +344,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       tcgen05_wait_st();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_remote(&p_full[b], 0);  // the leader's barrier: 4 warps from each CTA
+      // the leader's barrier: 4 warps from each CTA.  The waiter is in another CTA, so the arrive
+      // carries a release at cluster scope (the PTX memory model gives no cross-CTA ordering to a
+      // CTA-scope release); it costs ~850 cycles per arrive, which this variant can afford.
+      if (lane == 0) mbar_arrive_cluster(&p_full[b], 0);
     }
 
     if (ok && n > 0) {

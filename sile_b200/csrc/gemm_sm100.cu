@@ -502,6 +502,240 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   }
 }
 
+// ---- CTA-pair variant with the all-gather in its epilogue -------------------------------------
+// The 256 x 256 pair kernel above with a store epilogue built for the fused all-gather: each
+// epilogue warp converts its 32 rows x 256 columns of a tile into a 16 KiB staging buffer of its
+// own (four 128-byte-swizzled boxes), hands tensor memory back, and lane 0 issues one TMA store per
+// box and DESTINATION -- this GPU's C and every peer's, over NVLink -- starting with a different
+// destination for every tile.  The staging buffer holds the warp's whole share of the tile and the
+// tile has two accumulators, so the stores of tile i drain while tile i+1 is being computed and
+// tile i+2's main loop has already started; the warp only waits for them (for shared memory to have
+// been read) when it comes back with tile i+1.  With p destinations the stores are what bounds
+// the kernel (each GPU has to take in (p-1)/p of C), and an epilogue that waits for every box to
+// leave before it converts the next one -- as the wide kernel's 4 KiB staging makes it do -- keeps
+// tensor memory occupied and stalls the MMAs behind the NVLink queue.  4 ring stages of 32 KiB.
+constexpr int kAgStages = 4;
+constexpr int kAgStagingBytes = 4 * 4 * 4096;  // 4 epilogue warps x 4 boxes of 32 rows x 128 bytes
+constexpr int kAgSmemBytes = kAgStages * kPairStageBytes + kAgStagingBytes + 256 + 1024;
+
+template <typename OutT>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_tn_pair_ag_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p,
+                       const uint32_t idesc, const int vec_ok, int* __restrict__ status, const PeerOut peers,
+                       const __grid_constant__ OutMaps out_maps) {
+  static_assert(sizeof(OutT) == 2, "the staging layout assumes 16-bit outputs");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* staging = smem + kAgStages * kPairStageBytes;  // 1024-byte aligned: matches the store maps' swizzle
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + kAgStagingBytes);
+  uint64_t* empty_bar = full_bar + kAgStages;
+  uint64_t* tmem_full_bar = empty_bar + kAgStages;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tma_a);
+    prefetch_tensormap(&tma_b);
+    for (int s = 0; s < kAgStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], 8);  // 4 epilogue warps in each of the two CTAs
+    }
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(tmem_slot, kTmemCols);
+    tmem_relinquish<2>();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  const int m_blocks = (p.m_valid + kPairBM - 1) / kPairBM;
+  const int num_tiles = m_blocks * p.n_blocks;
+  const int num_kb = p.k_blocks_per_seg * p.num_segs;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        int m_blk, n_blk;
+        pair_tile_coords(t, p, m_blocks, m_blk, n_blk);
+        const int a_row = m_blk * kPairBM + static_cast<int>(rank) * 128;
+        const int b_row = n_blk * kBN + static_cast<int>(rank) * 128;
+        int seg = 0, kb_in_seg = 0;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait<true>(&empty_bar[stage], phase ^ 1u, status, SILE_ERR_TIMEOUT, 1 + 4 * rank)) { ok = false; break; }
+          uint8_t* sa = smem + stage * kPairStageBytes;
+          uint8_t* sb = sa + kPairABytes;
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * kPairStageBytes);
+          tma_load_2d_pair(sa, &tma_a, &full_bar[stage], 0, kb_in_seg * kBK, p.a_seg_row[seg] + a_row);
+          tma_load_2d_pair(sb, &tma_b, &full_bar[stage], 0, kb_in_seg * kBK, p.b_seg_row[seg] + b_row);
+          if (++kb_in_seg == p.k_blocks_per_seg) { kb_in_seg = 0; ++seg; }
+          if (++stage == kAgStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader) {
+      const uint32_t el = elect_one() ? 1u : 0u;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!__all_sync(0xffffffffu, mbar_wait<true>(&tmem_empty_bar[buf], acc_phase ^ 1u, status, SILE_ERR_TIMEOUT, 2))) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * kBN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!__all_sync(0xffffffffu, mbar_wait<true>(&full_bar[stage], phase, status, SILE_ERR_TIMEOUT, 3))) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
+          const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(sa + kPairABytes, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) umma_ss_f16_if<2>(el, tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_if<2>(el, pair_addr(&empty_bar[stage], 0));
+          umma_commit_if<2>(el, pair_addr(&empty_bar[stage], 1));
+          if (++stage == kAgStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) {
+          umma_commit_if<2>(el, pair_addr(&tmem_full_bar[buf], 0));
+          umma_commit_if<2>(el, pair_addr(&tmem_full_bar[buf], 1));
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (both CTAs) ----------------
+    const int quarter = warp & 3;
+    uint8_t* stage = staging + quarter * (4 * 4096);
+    const uint32_t stage_addr = smem_u32(stage);
+    int it = 0;
+    bool ok = true;
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+      int m_blk, n_blk;
+      pair_tile_coords(t, p, m_blocks, m_blk, n_blk);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait<true>(&tmem_full_bar[buf], acc_phase, status, SILE_ERR_TIMEOUT, 4 + 4 * rank)) { ok = false; }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row0 = m_blk * kPairBM + static_cast<int>(rank) * 128;
+      const int row = row0 + quarter * 32 + lane;
+      const int col_base = n_blk * kBN;
+      const bool tile_fast = vec_ok && !p.masked && (row0 + 128 <= p.m_valid) && (col_base + kBN <= p.n_valid);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
+      if (tile_fast) {
+        // the stores of this warp's previous tile must have been read out of the staging buffer
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+#pragma unroll 1
+        for (int b = 0; b < 4; ++b) {  // boxes of 64 columns
+          uint32_t r[32], r2[32];
+          tmem_ld_32x32b_x32(taddr + b * 64, r);
+          tmem_ld_32x32b_x32(taddr + b * 64 + 32, r2);
+          tcgen05_wait_ld();
+          if (b == 3) {
+            // last read of this accumulator: hand tensor memory back before the stores are issued
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(&tmem_empty_bar[buf], 0);
+          }
+          // row `lane` of the box: eight 16-byte chunks, chunk j stored at position j ^ (lane & 7)
+          const uint32_t row_addr = stage_addr + b * 4096 + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t* src = (j < 4) ? (r + 8 * j) : (r2 + 8 * (j - 4));
+            uint32_t v0, v1, v2, v3;
+            if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+              v0 = pack_bf16x2(__uint_as_float(src[0]), __uint_as_float(src[1]));
+              v1 = pack_bf16x2(__uint_as_float(src[2]), __uint_as_float(src[3]));
+              v2 = pack_bf16x2(__uint_as_float(src[4]), __uint_as_float(src[5]));
+              v3 = pack_bf16x2(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            } else {
+              __half2 h0 = __floats2half2_rn(__uint_as_float(src[0]), __uint_as_float(src[1]));
+              __half2 h1 = __floats2half2_rn(__uint_as_float(src[2]), __uint_as_float(src[3]));
+              __half2 h2 = __floats2half2_rn(__uint_as_float(src[4]), __uint_as_float(src[5]));
+              __half2 h3 = __floats2half2_rn(__uint_as_float(src[6]), __uint_as_float(src[7]));
+              v0 = *reinterpret_cast<uint32_t*>(&h0); v1 = *reinterpret_cast<uint32_t*>(&h1);
+              v2 = *reinterpret_cast<uint32_t*>(&h2); v3 = *reinterpret_cast<uint32_t*>(&h3);
+            }
+            const uint32_t dst = row_addr + ((j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v0), "r"(v1), "r"(v2), "r"(v3) : "memory");
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          // destinations in an order that rotates with the tile, so the GPUs do not all send to
+          // the same peer at the same moment
+          int d = (peers.first + t) % peers.count;
+          for (int i = 0; i < peers.count; ++i) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) tma_store_2d(&out_maps.map[d], stage + b * 4096, col_base + b * 64, row0 + quarter * 32);
+            if (++d == peers.count) d = 0;
+          }
+          tma_store_commit();
+        }
+      } else {
+#pragma unroll 1
+        for (int ch = 0; ch < kBN / 32; ++ch) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + ch * 32, r);
+          tcgen05_wait_ld();
+          if (col_base + ch * 32 < p.n_valid) {
+            int d = peers.first;
+            for (int i = 0; i < peers.count; ++i) {
+              store_chunk<OutT>(static_cast<OutT*>(peers.ptr[d]), p, row, col_base + ch * 32, r, false);
+              if (++d == peers.count) d = 0;
+            }
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(&tmem_empty_bar[buf], 0);
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();  // every store of this warp has been written out
+    __syncwarp();
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    if (*reinterpret_cast<volatile int*>(status) != 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) {
+      }
+    }
+    tmem_dealloc<2>(tmem_base, kTmemCols);
+  }
+}
+
 // ---- wide CTA-pair variant -----------------------------------------------------------
 // Same pairing, but one pair owns a 256 x 512 tile: per 64-wide k block each CTA stages its 128
 // rows of A once and its 128-row shares of TWO 256-column B halves (48 KiB per stage, 4 stages),
@@ -799,30 +1033,51 @@ __global__ void split_rows_kernel(const float* __restrict__ src, int64_t ld, __n
 }
 
 // B: [K,N] f32 row-major -> hi/lo [N,Kp] bf16 (transposed to K-major), zero for k >= k_eff.
-// Block = 32 x 8 threads, tile = 64 (k) x 32 (n).
+// Block = 32 x 8 threads, tile = 64 (k) x 64 (n).  Reads run along n, 8 bytes per thread and 256
+// bytes per warp and k row, eight rows in flight per thread; after the transpose through shared
+// memory a thread owns 8 consecutive k of one n and writes them as one 16-byte store per plane,
+// eight threads covering the tile's 128 bytes of a row.
 __global__ void split_transpose_kernel(const float* __restrict__ src, int64_t ld, __nv_bfloat16* __restrict__ hi,
-                                       __nv_bfloat16* __restrict__ lo, int n, int k_eff, int kp) {
-  __shared__ float tile[64][33];
-  const int n0 = blockIdx.x * 32;
+                                       __nv_bfloat16* __restrict__ lo, int n, int k_eff, int kp, int vec2) {
+  __shared__ float tile[64][65];
+  const int n0 = blockIdx.x * 64;
   const int k0 = blockIdx.y * 64;
   const int tx = threadIdx.x, ty = threadIdx.y;
+  float2 v[8];
 #pragma unroll
-  for (int kk = ty; kk < 64; kk += 8) {
-    const int k = k0 + kk, col = n0 + tx;
-    tile[kk][tx] = (k < k_eff && col < n) ? __ldg(src + static_cast<int64_t>(k) * ld + col) : 0.0f;
+  for (int i = 0; i < 8; ++i) {
+    const int k = k0 + ty + 8 * i, col = n0 + 2 * tx;
+    const float* s = src + static_cast<int64_t>(k) * ld + col;
+    if (k < k_eff && vec2 && col + 1 < n) {
+      v[i] = __ldg(reinterpret_cast<const float2*>(s));
+    } else {
+      v[i].x = (k < k_eff && col < n) ? __ldg(s) : 0.0f;
+      v[i].y = (k < k_eff && col + 1 < n) ? __ldg(s + 1) : 0.0f;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    tile[ty + 8 * i][2 * tx] = v[i].x;
+    tile[ty + 8 * i][2 * tx + 1] = v[i].y;
   }
   __syncthreads();
+  const int kc = (tx & 7) * 8;  // first of this thread's 8 k values
 #pragma unroll
-  for (int nn = ty; nn < 32; nn += 8) {
+  for (int half = 0; half < 2; ++half) {
+    const int nn = half * 32 + ty * 4 + (tx >> 3);  // row of the transposed tile
     const int col = n0 + nn;
     if (col < n) {
-      const float x0 = tile[2 * tx][nn], x1 = tile[2 * tx + 1][nn];
-      const __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
-      const uint32_t hv = static_cast<uint32_t>(__bfloat16_as_ushort(h0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(h1)) << 16);
-      const uint32_t lv = pack_bf16x2(x0 - __bfloat162float(h0), x1 - __bfloat162float(h1));
-      const int64_t o = static_cast<int64_t>(col) * kp + k0 + 2 * tx;
-      *reinterpret_cast<uint32_t*>(hi + o) = hv;
-      *reinterpret_cast<uint32_t*>(lo + o) = lv;
+      uint32_t h[4], l[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float x0 = tile[kc + 2 * i][nn], x1 = tile[kc + 2 * i + 1][nn];
+        const __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
+        h[i] = static_cast<uint32_t>(__bfloat16_as_ushort(h0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(h1)) << 16);
+        l[i] = pack_bf16x2(x0 - __bfloat162float(h0), x1 - __bfloat162float(h1));
+      }
+      const int64_t o = static_cast<int64_t>(col) * kp + k0 + kc;
+      *reinterpret_cast<uint4*>(hi + o) = make_uint4(h[0], h[1], h[2], h[3]);
+      *reinterpret_cast<uint4*>(lo + o) = make_uint4(l[0], l[1], l[2], l[3]);
     }
   }
 }
@@ -975,6 +1230,73 @@ int launch_pair(int out_dtype, const CUtensorMap& ta, const CUtensorMap& tb, voi
   }
 }
 
+// The all-gather pair kernel: resident clusters (cached per device) and launch.
+template <typename OutT>
+int ag_max_clusters() {
+  static int cache[kMaxDevices];
+  static bool known[kMaxDevices] = {};
+  const int slot = current_device_slot();
+  if (known[slot]) return cache[slot];
+  known[slot] = true;
+  int& max_clusters = cache[slot];
+  auto fn = &gemm_tn_pair_ag_kernel<OutT>;
+  if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kAgSmemBytes) != cudaSuccess) {
+    cudaGetLastError();
+    return max_clusters = 0;
+  }
+  int sms = 148, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(2 * (sms / 2));
+  cfg.blockDim = dim3(kNumThreads);
+  cfg.dynamicSmemBytes = kAgSmemBytes;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  return max_clusters = n;
+}
+
+template <typename OutT>
+int launch_pair_ag(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& gp, uint32_t idesc, int vec_ok, int* status,
+                   cudaStream_t stream, const PeerOut& peers, const OutMaps& out_maps) {
+  const int m_blocks = (gp.m_valid + kPairBM - 1) / kPairBM;
+  const int tiles = m_blocks * gp.n_blocks;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(2 * std::min(tiles, ag_max_clusters<OutT>()));
+  cfg.blockDim = dim3(kNumThreads);
+  cfg.dynamicSmemBytes = kAgSmemBytes;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, &gemm_tn_pair_ag_kernel<OutT>, ta, tb, gp, idesc, vec_ok, status, peers, out_maps));
+  note_kernel("gemm_tn_pair_ag_kernel<16-bit>", cfg.gridDim.x, cfg.blockDim.x, cfg.dynamicSmemBytes);
+  return SILE_OK;
+}
+
+// SILE_CUDA_GEMM_AG_KERNEL = wide | pair picks the kernel of the fused GEMM + all-gather (tuning).
+int forced_ag_kernel() {
+  const char* e = getenv("SILE_CUDA_GEMM_AG_KERNEL");
+  if (!e) return 0;
+  if (!strcmp(e, "wide")) return 1;
+  if (!strcmp(e, "pair")) return 2;
+  return 0;
+}
+
 // SILE_CUDA_GEMM_KERNEL = single | pair | wide overrides the kernel choice (tuning, tests).
 // Read on every launch so a process can switch.
 int forced_kernel() {
@@ -1065,7 +1387,15 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
   } else if (forced == 2 || (forced == 0 && e.n_valid <= kBN && tiles_pair >= kMinPairTiles)) {
     use_pair = e.m_valid > kBM && pair_max_clusters_for<false>(p.out_dtype) > 0;
   }
-  use_pair = use_pair || use_wide;
+  // Fused GEMM + all-gather: the 256 x 256 pair kernel whose epilogue stages whole tiles and lets
+  // the stores to every destination drain under the following tiles (16-bit outputs); the wide
+  // kernel otherwise, or when asked for.
+  bool use_ag = false;
+  if (p.num_peers > 0 && p.out_dtype != SILE_DTYPE_F32 && forced_ag_kernel() != 1 && e.m_valid > kBM) {
+    use_ag = (p.out_dtype == SILE_DTYPE_BF16 ? ag_max_clusters<__nv_bfloat16>() : ag_max_clusters<__half>()) > 0;
+    if (use_ag) use_wide = false;
+  }
+  use_pair = use_pair || use_wide || use_ag;
   const uint32_t box_a[2] = {kBK, kBM};
   const uint32_t box_b[2] = {kBK, use_pair ? 128u : static_cast<uint32_t>(kBN)};
 
@@ -1088,10 +1418,11 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
       SILE_CUDA_TRY(cudaGetLastError());
     }
     {
-      dim3 grid(static_cast<unsigned>((p.n + 31) / 32), static_cast<unsigned>(e.kp / 64));
+      dim3 grid(static_cast<unsigned>((p.n + 63) / 64), static_cast<unsigned>(e.kp / 64));
+      const int vec2 = (p.n % 2 == 0) && (reinterpret_cast<uintptr_t>(p.b) % 8 == 0);
       split_transpose_kernel<<<grid, dim3(32, 8), 0, stream>>>(static_cast<const float*>(p.b), p.n, b_hi, b_lo,
                                                                static_cast<int>(p.n), static_cast<int>(e.k_eff),
-                                                               static_cast<int>(e.kp));
+                                                               static_cast<int>(e.kp), vec2);
       SILE_CUDA_TRY(cudaGetLastError());
     }
     // Tensor maps over the stacked planes: rows [0,M) = hi, [M,2M) = lo.
@@ -1139,7 +1470,7 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
   const int vec_ok = (reinterpret_cast<uintptr_t>(p.c) % 16 == 0) && ((gp.ldc * out_elt) % 16 == 0);
   PeerOut peers{};
   if (p.num_peers > 0) {
-    if (!use_wide) return fail(SILE_ERR_UNSUPPORTED, "matmul: the fused all-gather epilogue needs the wide pair kernel (M > 128, N > 256 per rank)");
+    if (!use_wide && !use_ag) return fail(SILE_ERR_UNSUPPORTED, "matmul: the fused all-gather epilogue needs a CTA-pair kernel (M > 128)");
     for (int i = 0; i < p.num_peers; ++i) peers.ptr[i] = p.peer_c[i];
     peers.count = p.num_peers;
     peers.first = p.peer_first;
@@ -1150,7 +1481,7 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
   }
   if (use_pair) {
     const uint32_t idesc2 = make_idesc_f16(kPairBM, kBN, bf16, false, false);
-    if (!use_wide) return launch_pair<false>(p.out_dtype, ta, tb, p.c, gp, idesc2, vec_ok, status, stream, peers, nullptr);
+    if (!use_wide && !use_ag) return launch_pair<false>(p.out_dtype, ta, tb, p.c, gp, idesc2, vec_ok, status, stream, peers, nullptr);
     static OutMaps zero_maps{};
     OutMaps maps = zero_maps;
     if (vec_ok) {
@@ -1164,6 +1495,10 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
       const uint32_t obox[2] = {static_cast<uint32_t>(128 / out_elt), 32};
       for (int i = 0; i < peers.count; ++i)
         if (int rc = encode_tensor_map(&maps.map[i], odt, 2, peers.ptr[i], odims, ostride, obox, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+    }
+    if (use_ag) {
+      if (p.out_dtype == SILE_DTYPE_BF16) return launch_pair_ag<__nv_bfloat16>(ta, tb, gp, idesc2, vec_ok, status, stream, peers, maps);
+      return launch_pair_ag<__half>(ta, tb, gp, idesc2, vec_ok, status, stream, peers, maps);
     }
     return launch_pair<true>(p.out_dtype, ta, tb, p.c, gp, idesc2, vec_ok, status, stream, peers, &maps);
   }
@@ -1293,9 +1628,10 @@ extern "C" int sile_cuda_matmul_f32_noalloc(const float* a, const float* b, floa
     split_rows_kernel<<<blocks, threads, 0, stream>>>(a, k, a_hi, a_lo, static_cast<int>(m), static_cast<int>(e.k_eff),
                                                       static_cast<int>(e.kp), vec4);
     SILE_CUDA_TRY(cudaGetLastError());
-    dim3 grid(static_cast<unsigned>((n + 31) / 32), static_cast<unsigned>(e.kp / 64));
+    dim3 grid(static_cast<unsigned>((n + 63) / 64), static_cast<unsigned>(e.kp / 64));
+    const int vec2 = (n % 2 == 0) && (reinterpret_cast<uintptr_t>(b) % 8 == 0);
     split_transpose_kernel<<<grid, dim3(32, 8), 0, stream>>>(b, n, b_hi, b_lo, static_cast<int>(n), static_cast<int>(e.k_eff),
-                                                             static_cast<int>(e.kp));
+                                                             static_cast<int>(e.kp), vec2);
     SILE_CUDA_TRY(cudaGetLastError());
   }
 

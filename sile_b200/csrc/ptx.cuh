@@ -67,15 +67,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// As mbar_arrive_cluster below but with the default (release at CTA scope) semantics.  Enough when
-// the data handed over lives in tensor memory, whose ordering comes from tcgen05.wait / tcgen05.fence;
-// the cluster-scope release was measured at ~850 cycles per arrive inside the attention loop.
-__device__ __forceinline__ void mbar_arrive_remote(uint64_t* local_bar, uint32_t cta_rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_bar)), "r"(cta_rank));
-  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
-}
-// Arrive on a barrier that lives in the shared memory of CTA `cta_rank` of this cluster.
+// Arrive on a barrier that lives in the shared memory of CTA `cta_rank` of this cluster, with a
+// release at cluster scope: the only form that orders this thread's earlier writes before a
+// waiter in ANOTHER CTA (a CTA-scope release does not, under the PTX memory model).
 __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* local_bar, uint32_t cta_rank) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_bar)), "r"(cta_rank));

@@ -206,13 +206,17 @@ def test_g3_bf16_8192_sampled_tiles_and_linearity(sb, oracle):
     assert torch.equal(dc2, dc * 2)
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_fused_allgather_epilogue_on_one_gpu(sb, oracle, world):
+@pytest.mark.parametrize("ag_kernel", ["pair", "wide"])
+@pytest.mark.parametrize("world,m", [(2, 512), (4, 512), (8, 1000)])
+def test_fused_allgather_epilogue_on_one_gpu(sb, oracle, monkeypatch, world, m, ag_kernel):
     """The GEMM whose epilogue stores its column block into every rank's buffer, with the ranks
     played one after another on a single GPU (no kernel waits on another): afterwards every
-    buffer holds the whole product."""
+    buffer holds the whole product.  Both kernels that carry the fused epilogue -- the 256 x 256
+    pair kernel that stages whole tiles (the default) and the wide one -- and a row count that
+    leaves a ragged last tile (per-thread stores to every destination)."""
     import torch
-    m, n, k = 512, 2048, 256
+    monkeypatch.setenv("SILE_CUDA_GEMM_AG_KERNEL", ag_kernel)
+    n, k = 2048, 256
     a32 = normal((m, k), 40, 1.0 / np.sqrt(k))
     b32 = normal((k, n), 41, 1.0 / np.sqrt(k))
     ta, a_up = to_bf16_bits(a32)
@@ -224,6 +228,8 @@ def test_fused_allgather_epilogue_on_one_gpu(sb, oracle, world):
     w = n // world
     for rank in range(world):
         sb.matmul_allgather(da, db[rank * w:(rank + 1) * w].contiguous(), ptrs, rank, n, torch.bfloat16)
+    chosen = sb._lib.lib().sile_cuda_last_kernel().decode()
+    assert chosen.startswith("gemm_tn_pair_ag_kernel" if ag_kernel == "pair" else "gemm_tn_pair_wide_kernel"), chosen
     sb.synchronize()
     want = oracle.matmul(a_up, b_up, 1, 1, 1)
     for b in bufs:
