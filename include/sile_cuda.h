@@ -175,12 +175,14 @@ int sile_cuda_matmul_shard(const SileKernelDesc* desc, const void* a, const void
  * `rank` of `world` (<= 8) computes its block and stores every element into the
  * full [M, n_total] row-major buffer of EVERY rank.  c_peers[i] is the base of
  * rank i's buffer as mapped into this process (for instance the buffer_ptrs of
- * a torch symmetric-memory allocation; c_peers[rank] is the local one).  Stores
- * to peers travel over NVLink as plain st.global from the epilogue warps; the
- * kernel waits on no other GPU.  When the call has completed on every rank and
- * the ranks have synchronised (the caller's barrier), each holds the whole C.
- * 16-bit operands, column-major B, N divisible by world, M > 128 and more than
- * 256 columns per rank. */
+ * a torch symmetric-memory allocation; c_peers[rank] is the local one).  Whole tiles leave the
+ * epilogue as TMA stores, one per 32-row x 128-byte box and destination (the peers' over NVLink),
+ * ragged or launch-masked tiles as st.global from the epilogue warps; the kernel waits on no
+ * other GPU.  When the call has completed on every rank and the ranks have synchronised (the
+ * caller's barrier), each holds the whole C.  16-bit operands, column-major B, N divisible by
+ * world, M > 128.  With 16-bit outputs the 256 x 256 CTA-pair kernel built for this epilogue
+ * runs (stores drain under the next tile); f32 outputs take the 256 x 512 kernel and need more
+ * than 256 columns per rank.  SILE_FLAG_ACCUMULATE is refused here. */
 int sile_cuda_matmul_allgather(const SileKernelDesc* desc, const void* a, const void* b_shard,
                                void* const* c_peers, int32_t world, int32_t rank, int64_t m,
                                int64_t n_total, int64_t k, void* stream);

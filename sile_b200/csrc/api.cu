@@ -477,12 +477,13 @@ int launch_host_matmul_pipelined(const SileKernelDesc* d, void* const* host, con
   struct Streams {
     int device = -1;
     cudaStream_t in = nullptr, run = nullptr, out = nullptr;
+    std::vector<cudaEvent_t> events;  // reused by every call of this thread
   };
   static thread_local Streams cached;
   int dev_now = 0;
   SILE_CUDA_TRY(cudaGetDevice(&dev_now));
   if (cached.device != dev_now) {
-    cached = Streams{};
+    cached = Streams{};  // (streams and events of a previously used device are left to that device)
     SILE_CUDA_TRY(cudaStreamCreateWithFlags(&cached.in, cudaStreamNonBlocking));
     SILE_CUDA_TRY(cudaStreamCreateWithFlags(&cached.run, cudaStreamNonBlocking));
     SILE_CUDA_TRY(cudaStreamCreateWithFlags(&cached.out, cudaStreamNonBlocking));
@@ -505,17 +506,19 @@ int launch_host_matmul_pipelined(const SileKernelDesc* d, void* const* host, con
     chunk_rows.push_back(left);
   }
   void *da = nullptr, *db = nullptr, *dc = nullptr;
-  std::vector<cudaEvent_t> events;
+  size_t events_used = 0;
   int rc = SILE_OK;
   auto check = [&](cudaError_t e, const char* what) {
     if (e != cudaSuccess && rc == SILE_OK) rc = fail(SILE_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
     return e == cudaSuccess;
   };
   auto new_event = [&]() {
-    cudaEvent_t ev = nullptr;
-    check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
-    events.push_back(ev);
-    return ev;
+    if (events_used == cached.events.size()) {
+      cudaEvent_t ev = nullptr;
+      check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
+      cached.events.push_back(ev);
+    }
+    return cached.events[events_used++];
   };
   if (rc == SILE_OK) rc = pool_alloc(&da, static_cast<size_t>(m * k) * in_sz, s_in);
   if (rc == SILE_OK) rc = pool_alloc(&db, static_cast<size_t>(k * n) * in_sz, s_in);
@@ -553,8 +556,6 @@ int launch_host_matmul_pipelined(const SileKernelDesc* d, void* const* host, con
   for (void* ptr : {da, db, dc})
     if (ptr) cudaFreeAsync(ptr, s_in);
   cudaStreamSynchronize(s_in);
-  for (cudaEvent_t ev : events)
-    if (ev) cudaEventDestroy(ev);
   return rc;
 }
 

@@ -4,13 +4,14 @@
 // (crates/sile-tile-ir/src/passes/lowering/canonical_matmul.rs:24-444) and of its
 // OpenMP tile loop (crates/sile-backend/src/cpu/codegen.rs:517-551).
 //
-// One persistent, warp-specialised kernel:
-//   warp 0      TMA producer   global -> 128B-swizzled shared-memory ring
-//   warp 1      MMA issuer     tcgen05.mma kind::f16, f32 accumulators in TMEM
-//   warps 2..5  epilogue       tcgen05.ld -> convert -> global
-// CTA tile 128 x 256 x 64 (16-bit operands), 4 ring stages (48 KiB each), two
-// TMEM accumulators (2 x 256 columns) so the epilogue of tile i overlaps the
-// main loop of tile i+1.
+// Four persistent, warp-specialised kernels share one structure -- warp 0 TMA producer (global ->
+// 128B-swizzled shared-memory ring), warp 1 tcgen05.mma kind::f16 issuer with f32 accumulators in
+// TMEM, the remaining warps epilogue (tcgen05.ld -> convert -> global):
+//   gemm_tn_kernel            one CTA, 128 x 256 x 64 tiles, two accumulators
+//   gemm_tn_pair_kernel       CTA pair (cta_group::2), 256 x 256 x 64, two accumulators
+//   gemm_tn_pair_wide_kernel  CTA pair, 256 x 512 x 64, one accumulator, TMA-store epilogue
+//   gemm_tn_pair_ag_kernel    CTA pair, 256 x 256 x 64, TMA stores to every rank's C (all-gather)
+// gemm_launch picks one by problem shape; see the comments at each kernel.
 //
 // f32 inputs are not fed to the tensor cores as tf32.  Each f32 value x is split
 // into bf16 hi = rn(x) and lo = rn(x - hi); the product is formed as
@@ -23,6 +24,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -504,26 +506,53 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 
 // ---- CTA-pair variant with the all-gather in its epilogue -------------------------------------
 // The 256 x 256 pair kernel above with a store epilogue built for the fused all-gather: each
-// epilogue warp converts its 32 rows x 256 columns of a tile into a 16 KiB staging buffer of its
-// own (four 128-byte-swizzled boxes), hands tensor memory back, and lane 0 issues one TMA store per
-// box and DESTINATION -- this GPU's C and every peer's, over NVLink -- starting with a different
-// destination for every tile.  The staging buffer holds the warp's whole share of the tile and the
-// tile has two accumulators, so the stores of tile i drain while tile i+1 is being computed and
-// tile i+2's main loop has already started; the warp only waits for them (for shared memory to have
-// been read) when it comes back with tile i+1.  With p destinations the stores are what bounds
-// the kernel (each GPU has to take in (p-1)/p of C), and an epilogue that waits for every box to
-// leave before it converts the next one -- as the wide kernel's 4 KiB staging makes it do -- keeps
-// tensor memory occupied and stalls the MMAs behind the NVLink queue.  4 ring stages of 32 KiB.
-constexpr int kAgStages = 4;
-constexpr int kAgStagingBytes = 4 * 4 * 4096;  // 4 epilogue warps x 4 boxes of 32 rows x 128 bytes
+// epilogue warp converts its 32 rows of a tile box by box (64 columns, 4 KiB, 128-byte swizzle)
+// through two staging boxes of its own, and lane 0 issues one TMA store per box and DESTINATION
+// -- this GPU's C and every peer's, over NVLink -- starting with a different destination for
+// every tile.  The tile has two accumulators, so the stores of tile i are issued and drain while
+// tile i+1 is being computed; a box is only waited for (for shared memory to have been read) when
+// its staging slot comes round again, two boxes later.  The ring keeps the six 32 KiB stages of
+// the plain pair kernel: a stage is consumed in 128 cycles, and with four (a first version, with a
+// whole-tile staging buffer instead) the main loop ran out of data in flight and the kernel was
+// no faster than the wide one.
+//
+// Work items are tiles or column slices of tiles.  The first `n1` tiles are cut into 2^s1 slices
+// of 256 >> s1 columns, the others into 2^s2 (s = 0, 1 or 2): a slice is an MMA of that N fed by
+// (128 >> s) rows of B per CTA and stored as (4 >> s) boxes.  Slicing the tiles of the last,
+// partly filled wave halves the time that wave takes (256 tiles on 74 CTA pairs are 3.5 waves
+// instead of 4), and slices finish -- and start crossing NVLink -- sooner than whole tiles.
+constexpr int kAgStages = 6;
+constexpr int kAgStagingBytes = 4 * 2 * 4096;  // 4 epilogue warps x 2 boxes of 32 rows x 128 bytes
 constexpr int kAgSmemBytes = kAgStages * kPairStageBytes + kAgStagingBytes + 256 + 1024;
+constexpr int kAgBBoxRows = 32;                // B rows per TMA load: the share of a quarter slice
+
+struct AgPlan {
+  int n1;             // tiles in the first group
+  int s1, s2;         // log2 of the slices per tile in the first / second group
+  int items;          // (n1 << s1) + ((tiles - n1) << s2)
+  uint32_t idesc[3];  // instruction descriptors for N = 256, 128, 64
+};
+
+__device__ __forceinline__ void ag_item(int i, const AgPlan& plan, int& tile, int& part, int& s) {
+  const int g1 = plan.n1 << plan.s1;
+  if (i < g1) {
+    s = plan.s1;
+    tile = i >> s;
+    part = i - (tile << s);
+  } else {
+    const int j = i - g1;
+    s = plan.s2;
+    tile = plan.n1 + (j >> s);
+    part = j - ((j >> s) << s);
+  }
+}
 
 template <typename OutT>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tn_pair_ag_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p,
-                       const uint32_t idesc, const int vec_ok, int* __restrict__ status, const PeerOut peers,
+                       const AgPlan plan, const int vec_ok, int* __restrict__ status, const PeerOut peers,
                        const __grid_constant__ OutMaps out_maps) {
-  static_assert(sizeof(OutT) == 2, "the staging layout assumes 16-bit outputs");
+  constexpr int kBoxCols = 128 / static_cast<int>(sizeof(OutT));  // columns in a 128-byte store box
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* staging = smem + kAgStages * kPairStageBytes;  // 1024-byte aligned: matches the store maps' swizzle
@@ -565,7 +594,7 @@ gemm_tn_pair_ag_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
   const int m_blocks = (p.m_valid + kPairBM - 1) / kPairBM;
-  const int num_tiles = m_blocks * p.n_blocks;
+  const int num_items = plan.items;
   const int num_kb = p.k_blocks_per_seg * p.num_segs;
 
   if (warp == 0) {
@@ -574,19 +603,25 @@ gemm_tn_pair_ag_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-        int m_blk, n_blk;
+      for (int i = cluster_id; i < num_items && ok; i += num_clusters) {
+        int t, part, s, m_blk, n_blk;
+        ag_item(i, plan, t, part, s);
         pair_tile_coords(t, p, m_blocks, m_blk, n_blk);
         const int a_row = m_blk * kPairBM + static_cast<int>(rank) * 128;
-        const int b_row = n_blk * kBN + static_cast<int>(rank) * 128;
+        const int b_share = 128 >> s;  // rows of B this CTA feeds to the pair's MMA
+        const int b_row = n_blk * kBN + part * (kBN >> s) + static_cast<int>(rank) * b_share;
+        const int b_loads = b_share / kAgBBoxRows;
+        const uint32_t tx = 2u * static_cast<uint32_t>(kPairABytes + b_share * kBK * 2);
         int seg = 0, kb_in_seg = 0;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait<true>(&empty_bar[stage], phase ^ 1u, status, SILE_ERR_TIMEOUT, 1 + 4 * rank)) { ok = false; break; }
           uint8_t* sa = smem + stage * kPairStageBytes;
           uint8_t* sb = sa + kPairABytes;
-          if (leader) mbar_expect_tx(&full_bar[stage], 2 * kPairStageBytes);
+          if (leader) mbar_expect_tx(&full_bar[stage], tx);
           tma_load_2d_pair(sa, &tma_a, &full_bar[stage], 0, kb_in_seg * kBK, p.a_seg_row[seg] + a_row);
-          tma_load_2d_pair(sb, &tma_b, &full_bar[stage], 0, kb_in_seg * kBK, p.b_seg_row[seg] + b_row);
+          for (int q = 0; q < b_loads; ++q)
+            tma_load_2d_pair(sb + q * (kAgBBoxRows * kBK * 2), &tma_b, &full_bar[stage], 0, kb_in_seg * kBK,
+                             p.b_seg_row[seg] + b_row + q * kAgBBoxRows);
           if (++kb_in_seg == p.k_blocks_per_seg) { kb_in_seg = 0; ++seg; }
           if (++stage == kAgStages) { stage = 0; phase ^= 1u; }
         }
@@ -601,7 +636,10 @@ gemm_tn_pair_ag_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+      for (int i = cluster_id; i < num_items && ok; i += num_clusters, ++it) {
+        int t, part, s;
+        ag_item(i, plan, t, part, s);
+        const uint32_t idesc = plan.idesc[s];
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!__all_sync(0xffffffffu, mbar_wait<true>(&tmem_empty_bar[buf], acc_phase ^ 1u, status, SILE_ERR_TIMEOUT, 2))) { ok = false; break; }
@@ -629,12 +667,14 @@ gemm_tn_pair_ag_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
   } else {
     // ---------------- epilogue (both CTAs) ----------------
     const int quarter = warp & 3;
-    uint8_t* stage = staging + quarter * (4 * 4096);
+    uint8_t* stage = staging + quarter * (2 * 4096);
     const uint32_t stage_addr = smem_u32(stage);
     int it = 0;
+    uint32_t slot = 0;  // staging box in turn, across items
     bool ok = true;
-    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
-      int m_blk, n_blk;
+    for (int i = cluster_id; i < num_items && ok; i += num_clusters, ++it) {
+      int t, part, s, m_blk, n_blk;
+      ag_item(i, plan, t, part, s);
       pair_tile_coords(t, p, m_blocks, m_blk, n_blk);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -644,32 +684,39 @@ gemm_tn_pair_ag_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       tcgen05_fence_after();
       const int row0 = m_blk * kPairBM + static_cast<int>(rank) * 128;
       const int row = row0 + quarter * 32 + lane;
-      const int col_base = n_blk * kBN;
-      const bool tile_fast = vec_ok && !p.masked && (row0 + 128 <= p.m_valid) && (col_base + kBN <= p.n_valid);
+      const int width = kBN >> s;
+      const int col_base = n_blk * kBN + part * width;
+      const bool tile_fast = vec_ok && !p.masked && (row0 + 128 <= p.m_valid) && (col_base + width <= p.n_valid);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
-      if (tile_fast) {
-        // the stores of this warp's previous tile must have been read out of the staging buffer
-        if (lane == 0) tma_store_wait_read<0>();
-        __syncwarp();
+      if (tile_fast && !p.accumulate) {
+        // destinations in an order that rotates with the item, so the GPUs do not all send to
+        // the same peer at the same moment
+        const int d0 = (peers.first + i) % peers.count;
+        const int boxes = width / kBoxCols;
 #pragma unroll 1
-        for (int b = 0; b < 4; ++b) {  // boxes of 64 columns
-          uint32_t r[32], r2[32];
-          tmem_ld_32x32b_x32(taddr + b * 64, r);
-          tmem_ld_32x32b_x32(taddr + b * 64 + 32, r2);
+        for (int b = 0; b < boxes; ++b, slot ^= 1u) {  // boxes of 128 bytes x 32 rows
+          uint32_t r[32], r2[sizeof(OutT) == 2 ? 32 : 1];
+          tmem_ld_32x32b_x32(taddr + b * kBoxCols, r);
+          if constexpr (sizeof(OutT) == 2) tmem_ld_32x32b_x32(taddr + b * kBoxCols + 32, r2);
           tcgen05_wait_ld();
-          if (b == 3) {
+          if (b == boxes - 1) {
             // last read of this accumulator: hand tensor memory back before the stores are issued
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(&tmem_empty_bar[buf], 0);
           }
+          // the stores issued from this slot two boxes ago must have been read out of it
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
           // row `lane` of the box: eight 16-byte chunks, chunk j stored at position j ^ (lane & 7)
-          const uint32_t row_addr = stage_addr + b * 4096 + lane * 128;
+          const uint32_t row_addr = stage_addr + slot * 4096 + lane * 128;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const uint32_t* src = (j < 4) ? (r + 8 * j) : (r2 + 8 * (j - 4));
             uint32_t v0, v1, v2, v3;
-            if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+            const uint32_t* src = (sizeof(OutT) == 4) ? (r + 4 * j) : (j < 4) ? (r + 8 * j) : (r2 + 8 * (j - 4));
+            if constexpr (sizeof(OutT) == 4) {
+              v0 = src[0]; v1 = src[1]; v2 = src[2]; v3 = src[3];
+            } else if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
               v0 = pack_bf16x2(__uint_as_float(src[0]), __uint_as_float(src[1]));
               v1 = pack_bf16x2(__uint_as_float(src[2]), __uint_as_float(src[3]));
               v2 = pack_bf16x2(__uint_as_float(src[4]), __uint_as_float(src[5]));
@@ -685,30 +732,27 @@ gemm_tn_pair_ag_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
             const uint32_t dst = row_addr + ((j ^ (lane & 7)) << 4);
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v0), "r"(v1), "r"(v2), "r"(v3) : "memory");
           }
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          // destinations in an order that rotates with the tile, so the GPUs do not all send to
-          // the same peer at the same moment
-          int d = (peers.first + t) % peers.count;
-          for (int i = 0; i < peers.count; ++i) {
-#pragma unroll
-            for (int b = 0; b < 4; ++b) tma_store_2d(&out_maps.map[d], stage + b * 4096, col_base + b * 64, row0 + quarter * 32);
-            if (++d == peers.count) d = 0;
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            int d = d0;
+            for (int q = 0; q < peers.count; ++q) {
+              tma_store_2d(&out_maps.map[d], stage + slot * 4096, col_base + b * kBoxCols, row0 + quarter * 32);
+              if (++d == peers.count) d = 0;
+            }
+            tma_store_commit();
           }
-          tma_store_commit();
         }
       } else {
 #pragma unroll 1
-        for (int ch = 0; ch < kBN / 32; ++ch) {
+        for (int ch = 0; ch < width / 32; ++ch) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(taddr + ch * 32, r);
           tcgen05_wait_ld();
           if (col_base + ch * 32 < p.n_valid) {
             int d = peers.first;
-            for (int i = 0; i < peers.count; ++i) {
-              store_chunk<OutT>(static_cast<OutT*>(peers.ptr[d]), p, row, col_base + ch * 32, r, false);
+            for (int q = 0; q < peers.count; ++q) {
+              store_chunk<OutT>(static_cast<OutT*>(peers.ptr[d]), p, row, col_base + ch * 32, r, tile_fast);
               if (++d == peers.count) d = 0;
             }
           }
@@ -1266,25 +1310,65 @@ int ag_max_clusters() {
   return max_clusters = n;
 }
 
+// How the tiles are cut into work items.  By default whole tiles for the full waves and, when
+// the last wave is partly filled, its tiles cut into the number of slices (2 or 4) that lets the
+// clusters finish it soonest; slices run a little below a whole tile's rate (more operand traffic
+// per flop), which the estimate charges.  SILE_CUDA_GEMM_AG_SPLIT = off | s1,s2,n1 overrides it
+// (tuning): the first n1 tiles in 2^s1 slices, the others in 2^s2; n1 < 0 = the full waves.
+AgPlan make_ag_plan(int tiles, int clusters, bool bf16) {
+  AgPlan plan{};
+  plan.idesc[0] = make_idesc_f16(kPairBM, kBN, bf16, false, false);
+  plan.idesc[1] = make_idesc_f16(kPairBM, kBN / 2, bf16, false, false);
+  plan.idesc[2] = make_idesc_f16(kPairBM, kBN / 4, bf16, false, false);
+  clusters = std::max(clusters, 1);
+  const int full = tiles / clusters * clusters;  // tiles in completely filled waves
+  const int rest = tiles - full;
+  int n1 = tiles, s1 = 0, s2 = 0;
+  if (rest > 0) {
+    const double cost[3] = {1.0, 1.08, 1.3};
+    double best = 1.0;
+    for (int s = 1; s <= 2; ++s) {
+      const int waves = ((rest << s) + clusters - 1) / clusters;
+      const double t = cost[s] * waves / (1 << s);
+      if (t < best - 0.05) { best = t; n1 = full; s2 = s; }
+    }
+  }
+  if (const char* e = getenv("SILE_CUDA_GEMM_AG_SPLIT")) {
+    int a = 0, b = 0, c = -1;
+    if (!strcmp(e, "off")) {
+      n1 = tiles; s1 = 0; s2 = 0;
+    } else if (sscanf(e, "%d,%d,%d", &a, &b, &c) >= 2 && a >= 0 && a <= 2 && b >= 0 && b <= 2) {
+      s1 = a; s2 = b;
+      n1 = (c < 0 || c > tiles) ? full : c;
+    }
+  }
+  plan.n1 = n1; plan.s1 = s1; plan.s2 = s2;
+  plan.items = (n1 << s1) + ((tiles - n1) << s2);
+  return plan;
+}
+
 template <typename OutT>
-int launch_pair_ag(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& gp, uint32_t idesc, int vec_ok, int* status,
+int launch_pair_ag(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& gp, bool bf16, int vec_ok, int* status,
                    cudaStream_t stream, const PeerOut& peers, const OutMaps& out_maps) {
   const int m_blocks = (gp.m_valid + kPairBM - 1) / kPairBM;
   const int tiles = m_blocks * gp.n_blocks;
+  const int max_clusters = ag_max_clusters<OutT>();
+  const AgPlan plan = make_ag_plan(tiles, max_clusters, bf16);
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
-  cfg.gridDim = dim3(2 * std::min(tiles, ag_max_clusters<OutT>()));
+  cfg.gridDim = dim3(2 * std::min(plan.items, max_clusters));
   cfg.blockDim = dim3(kNumThreads);
   cfg.dynamicSmemBytes = kAgSmemBytes;
   cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, &gemm_tn_pair_ag_kernel<OutT>, ta, tb, gp, idesc, vec_ok, status, peers, out_maps));
-  note_kernel("gemm_tn_pair_ag_kernel<16-bit>", cfg.gridDim.x, cfg.blockDim.x, cfg.dynamicSmemBytes);
+  SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, &gemm_tn_pair_ag_kernel<OutT>, ta, tb, gp, plan, vec_ok, status, peers, out_maps));
+  note_kernel(sizeof(OutT) == 4 ? "gemm_tn_pair_ag_kernel<float>" : "gemm_tn_pair_ag_kernel<16-bit>", cfg.gridDim.x, cfg.blockDim.x,
+              cfg.dynamicSmemBytes);
   return SILE_OK;
 }
 
@@ -1305,6 +1389,7 @@ int forced_kernel() {
   if (!strcmp(e, "single")) return 1;
   if (!strcmp(e, "pair")) return 2;
   if (!strcmp(e, "wide")) return 3;
+  if (!strcmp(e, "sliced")) return 4;
   return 0;
 }
 
@@ -1391,13 +1476,15 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
   // the stores to every destination drain under the following tiles (16-bit outputs); the wide
   // kernel otherwise, or when asked for.
   bool use_ag = false;
-  if (p.num_peers > 0 && p.out_dtype != SILE_DTYPE_F32 && forced_ag_kernel() != 1 && e.m_valid > kBM) {
-    use_ag = (p.out_dtype == SILE_DTYPE_BF16 ? ag_max_clusters<__nv_bfloat16>() : ag_max_clusters<__half>()) > 0;
+  if (e.m_valid > kBM && ((p.num_peers > 0 && forced_ag_kernel() != 1) || (p.num_peers == 0 && forced == 4))) {
+    use_ag = (p.out_dtype == SILE_DTYPE_F32    ? ag_max_clusters<float>()
+              : p.out_dtype == SILE_DTYPE_BF16 ? ag_max_clusters<__nv_bfloat16>()
+                                               : ag_max_clusters<__half>()) > 0;
     if (use_ag) use_wide = false;
   }
   use_pair = use_pair || use_wide || use_ag;
   const uint32_t box_a[2] = {kBK, kBM};
-  const uint32_t box_b[2] = {kBK, use_pair ? 128u : static_cast<uint32_t>(kBN)};
+  const uint32_t box_b[2] = {kBK, use_ag ? static_cast<uint32_t>(kAgBBoxRows) : use_pair ? 128u : static_cast<uint32_t>(kBN)};
 
   if (p.in_dtype == SILE_DTYPE_F32) {
     if (e.k_eff == 0) {
@@ -1497,8 +1584,9 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
         if (int rc = encode_tensor_map(&maps.map[i], odt, 2, peers.ptr[i], odims, ostride, obox, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
     }
     if (use_ag) {
-      if (p.out_dtype == SILE_DTYPE_BF16) return launch_pair_ag<__nv_bfloat16>(ta, tb, gp, idesc2, vec_ok, status, stream, peers, maps);
-      return launch_pair_ag<__half>(ta, tb, gp, idesc2, vec_ok, status, stream, peers, maps);
+      if (p.out_dtype == SILE_DTYPE_F32) return launch_pair_ag<float>(ta, tb, gp, bf16, vec_ok, status, stream, peers, maps);
+      if (p.out_dtype == SILE_DTYPE_BF16) return launch_pair_ag<__nv_bfloat16>(ta, tb, gp, bf16, vec_ok, status, stream, peers, maps);
+      return launch_pair_ag<__half>(ta, tb, gp, bf16, vec_ok, status, stream, peers, maps);
     }
     return launch_pair<true>(p.out_dtype, ta, tb, p.c, gp, idesc2, vec_ok, status, stream, peers, &maps);
   }

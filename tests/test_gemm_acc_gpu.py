@@ -47,7 +47,7 @@ def test_golden_inputs_with_a_seed_through_the_exact_abi(sb):
     assert np.abs(c - (seed + product)).max() < 1e-4
 
 
-@pytest.mark.parametrize("kernel", ["auto", "single", "pair", "wide"])
+@pytest.mark.parametrize("kernel", ["auto", "single", "pair", "wide", "sliced"])
 @pytest.mark.parametrize("m,n,k,bm,bn,bk", [
     (130, 260, 70, 2, 4, 7),      # ragged everywhere, K remainder dropped
     (384, 768, 320, 64, 64, 32),  # whole CTA tiles: the vector store path

@@ -133,10 +133,11 @@ def test_bf16_shapes(sb, oracle, m, n, k, col_major):
     assert rel_err(got, want) < BF16_TOL
 
 
-@pytest.mark.parametrize("kernel", ["single", "pair", "wide"])
+@pytest.mark.parametrize("kernel", ["single", "pair", "wide", "sliced"])
 def test_every_kernel_variant(sb, oracle, kernel, monkeypatch):
-    """The single-CTA, CTA-pair (256x256) and wide CTA-pair (256x512) kernels on the same
-    problems: ragged f32 with a K remainder and a short grid, and bf16 with several tiles."""
+    """The single-CTA, CTA-pair (256x256), wide CTA-pair (256x512) and sliced CTA-pair (256x256
+    tiles cut into column slices, TMA-store epilogue) kernels on the same problems: ragged f32
+    with a K remainder and a short grid, and bf16 with several tiles."""
     monkeypatch.setenv("SILE_CUDA_GEMM_KERNEL", kernel)
     m, n, k, bm, bn, bk = 700, 1100, 328, 4, 4, 8
     a, b = uniform((m, k), 31), uniform((k, n), 32)
@@ -206,15 +207,20 @@ def test_g3_bf16_8192_sampled_tiles_and_linearity(sb, oracle):
     assert torch.equal(dc2, dc * 2)
 
 
-@pytest.mark.parametrize("ag_kernel", ["pair", "wide"])
+@pytest.mark.parametrize("ag_kernel", ["pair", "pair:off", "pair:1,0,3", "pair:2,1,2", "pair:0,2,1", "wide"])
 @pytest.mark.parametrize("world,m", [(2, 512), (4, 512), (8, 1000)])
 def test_fused_allgather_epilogue_on_one_gpu(sb, oracle, monkeypatch, world, m, ag_kernel):
     """The GEMM whose epilogue stores its column block into every rank's buffer, with the ranks
     played one after another on a single GPU (no kernel waits on another): afterwards every
     buffer holds the whole product.  Both kernels that carry the fused epilogue -- the 256 x 256
-    pair kernel that stages whole tiles (the default) and the wide one -- and a row count that
-    leaves a ragged last tile (per-thread stores to every destination)."""
+    pair kernel (the default) and the wide one -- and a row count that leaves a ragged last tile
+    (per-thread stores to every destination).  The pair kernel cuts tiles into column slices;
+    the suffix names the cut: the default plan, none, or `s1,s2,n1` = the first n1 tiles in 2^s1
+    slices and the others in 2^s2."""
     import torch
+    ag_kernel, _, split = ag_kernel.partition(":")
+    if split:
+        monkeypatch.setenv("SILE_CUDA_GEMM_AG_SPLIT", split)
     monkeypatch.setenv("SILE_CUDA_GEMM_AG_KERNEL", ag_kernel)
     n, k = 2048, 256
     a32 = normal((m, k), 40, 1.0 / np.sqrt(k))
@@ -239,6 +245,26 @@ def test_fused_allgather_epilogue_on_one_gpu(sb, oracle, monkeypatch, world, m, 
     sb.matmul(da, db, single, 1, 1, 1, b_layout=sb._lib.LAYOUT_COL_MAJOR).apply()
     sb.synchronize()
     assert torch.equal(single, bufs[0])      # sharding changes nothing, bit for bit
+
+
+@pytest.mark.parametrize("ag_kernel", ["pair", "wide"])
+def test_fused_allgather_epilogue_with_f32_outputs(sb, oracle, monkeypatch, ag_kernel):
+    """The same with f32 destinations (a 128-byte store box is 32 columns wide instead of 64)."""
+    import torch
+    monkeypatch.setenv("SILE_CUDA_GEMM_AG_KERNEL", ag_kernel)
+    world, m, n, k = 2, 768, 1536, 192
+    ta, a_up = to_bf16_bits(normal((m, k), 50, 1.0 / np.sqrt(k)))
+    tb, b_up = to_bf16_bits(normal((k, n), 51, 1.0 / np.sqrt(k)))
+    da, db = ta.cuda(), tb.t().contiguous().cuda()
+    bufs = [torch.full((m, n), 9.0, device="cuda", dtype=torch.float32) for _ in range(world)]
+    w = n // world
+    for rank in range(world):
+        sb.matmul_allgather(da, db[rank * w:(rank + 1) * w].contiguous(), [b.data_ptr() for b in bufs], rank, n, torch.float32)
+    chosen = sb._lib.lib().sile_cuda_last_kernel().decode()
+    assert chosen.startswith("gemm_tn_pair_ag_kernel<float>" if ag_kernel == "pair" else "gemm_tn_pair_wide_kernel"), chosen
+    sb.synchronize()
+    assert rel_err(bufs[0].cpu().numpy(), oracle.matmul(a_up, b_up, 1, 1, 1)) < 1e-5
+    assert torch.equal(bufs[0], bufs[1])
 
 
 @pytest.mark.parametrize("m", [4096, 4160, 4608])
@@ -270,7 +296,7 @@ def test_host_buffer_launch_pipelines_large_bf16_and_matches_device_launch(sb, m
     assert rel_err(c_host[:256].float().numpy(), ref.numpy()) < BF16_TOL
 
 
-@pytest.mark.parametrize("kernel", ["single", "wide"])
+@pytest.mark.parametrize("kernel", ["single", "wide", "sliced"])
 def test_f16_inputs_and_outputs(sb, kernel, monkeypatch):
     """fp16 operands (kind::f16 with the f16 input format) and fp16 / f32 outputs."""
     import torch
