@@ -10,7 +10,8 @@
 //   gemm_tn_kernel            one CTA, 128 x 256 x 64 tiles, two accumulators
 //   gemm_tn_pair_kernel       CTA pair (cta_group::2), 256 x 256 x 64, two accumulators
 //   gemm_tn_pair_wide_kernel  CTA pair, 256 x 512 x 64, one accumulator, TMA-store epilogue
-//   gemm_tn_pair_ag_kernel    CTA pair, 256 x 256 x 64, TMA stores to every rank's C (all-gather)
+//   gemm_tn_pair_sliced_kernel  CTA pair, 256 x 256 x 64 tiles that can be cut into column slices,
+//                             two accumulators, TMA stores to one or to every rank's C (all-gather)
 // gemm_launch picks one by problem shape; see the comments at each kernel.
 //
 // f32 inputs are not fed to the tensor cores as tf32.  Each f32 value x is split
@@ -504,17 +505,18 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   }
 }
 
-// ---- CTA-pair variant with the all-gather in its epilogue -------------------------------------
+// ---- CTA-pair variant with sliced tiles and a TMA-store epilogue for one or many destinations ----
 // The 256 x 256 pair kernel above with a store epilogue built for the fused all-gather: each
-// epilogue warp converts its 32 rows of a tile box by box (64 columns, 4 KiB, 128-byte swizzle)
+// epilogue warp converts its 32 rows of a tile box by box (128 bytes x 32 rows, 128-byte swizzle)
 // through two staging boxes of its own, and lane 0 issues one TMA store per box and DESTINATION
 // -- this GPU's C and every peer's, over NVLink -- starting with a different destination for
-// every tile.  The tile has two accumulators, so the stores of tile i are issued and drain while
+// every item.  The tile has two accumulators, so the stores of tile i are issued and drain while
 // tile i+1 is being computed; a box is only waited for (for shared memory to have been read) when
 // its staging slot comes round again, two boxes later.  The ring keeps the six 32 KiB stages of
-// the plain pair kernel: a stage is consumed in 128 cycles, and with four (a first version, with a
-// whole-tile staging buffer instead) the main loop ran out of data in flight and the kernel was
-// no faster than the wide one.
+// the plain pair kernel; with four (a first version, with a whole-tile staging buffer instead)
+// the main loop ran out of data in flight and the kernel was no faster than the wide one.
+// With a single destination it is also the fastest kernel for shapes whose 256 x 512 tiles fill
+// the CTA pairs' waves badly (gemm_launch compares the two).
 //
 // Work items are tiles or column slices of tiles.  The first `n1` tiles are cut into 2^s1 slices
 // of 256 >> s1 columns, the others into 2^s2 (s = 0, 1 or 2): a slice is an MMA of that N fed by
@@ -524,7 +526,13 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 constexpr int kAgStages = 6;
 constexpr int kAgStagingBytes = 4 * 2 * 4096;  // 4 epilogue warps x 2 boxes of 32 rows x 128 bytes
 constexpr int kAgSmemBytes = kAgStages * kPairStageBytes + kAgStagingBytes + 256 + 1024;
-constexpr int kAgBBoxRows = 32;                // B rows per TMA load: the share of a quarter slice
+
+// B through three tensor maps whose boxes are a CTA's share of a whole tile, a half and a quarter
+// (128, 64, 32 rows): one load per stage whatever the slice.  (Loading a whole tile's share as four
+// 32-row boxes cost a fifth of the kernel's throughput.)
+struct AgBMaps {
+  CUtensorMap map[3];
+};
 
 struct AgPlan {
   int n1;             // tiles in the first group
@@ -549,7 +557,7 @@ __device__ __forceinline__ void ag_item(int i, const AgPlan& plan, int& tile, in
 
 template <typename OutT>
 __global__ void __launch_bounds__(kNumThreads, 1)
-gemm_tn_pair_ag_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p,
+gemm_tn_pair_sliced_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ AgBMaps tma_b, const GemmParams p,
                        const AgPlan plan, const int vec_ok, int* __restrict__ status, const PeerOut peers,
                        const __grid_constant__ OutMaps out_maps) {
   constexpr int kBoxCols = 128 / static_cast<int>(sizeof(OutT));  // columns in a 128-byte store box
@@ -571,7 +579,7 @@ gemm_tn_pair_ag_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
 
   if (warp == 0 && lane == 0) {
     prefetch_tensormap(&tma_a);
-    prefetch_tensormap(&tma_b);
+    for (int s = 0; s < 3; ++s) prefetch_tensormap(&tma_b.map[s]);
     for (int s = 0; s < kAgStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -610,7 +618,7 @@ gemm_tn_pair_ag_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         const int a_row = m_blk * kPairBM + static_cast<int>(rank) * 128;
         const int b_share = 128 >> s;  // rows of B this CTA feeds to the pair's MMA
         const int b_row = n_blk * kBN + part * (kBN >> s) + static_cast<int>(rank) * b_share;
-        const int b_loads = b_share / kAgBBoxRows;
+        const CUtensorMap* b_map = &tma_b.map[s];  // one load per stage: the box is the share
         const uint32_t tx = 2u * static_cast<uint32_t>(kPairABytes + b_share * kBK * 2);
         int seg = 0, kb_in_seg = 0;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -619,9 +627,7 @@ gemm_tn_pair_ag_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
           uint8_t* sb = sa + kPairABytes;
           if (leader) mbar_expect_tx(&full_bar[stage], tx);
           tma_load_2d_pair(sa, &tma_a, &full_bar[stage], 0, kb_in_seg * kBK, p.a_seg_row[seg] + a_row);
-          for (int q = 0; q < b_loads; ++q)
-            tma_load_2d_pair(sb + q * (kAgBBoxRows * kBK * 2), &tma_b, &full_bar[stage], 0, kb_in_seg * kBK,
-                             p.b_seg_row[seg] + b_row + q * kAgBBoxRows);
+          tma_load_2d_pair(sb, b_map, &full_bar[stage], 0, kb_in_seg * kBK, p.b_seg_row[seg] + b_row);
           if (++kb_in_seg == p.k_blocks_per_seg) { kb_in_seg = 0; ++seg; }
           if (++stage == kAgStages) { stage = 0; phase ^= 1u; }
         }
@@ -1283,7 +1289,7 @@ int ag_max_clusters() {
   if (known[slot]) return cache[slot];
   known[slot] = true;
   int& max_clusters = cache[slot];
-  auto fn = &gemm_tn_pair_ag_kernel<OutT>;
+  auto fn = &gemm_tn_pair_sliced_kernel<OutT>;
   if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kAgSmemBytes) != cudaSuccess) {
     cudaGetLastError();
     return max_clusters = 0;
@@ -1312,9 +1318,33 @@ int ag_max_clusters() {
 
 // How the tiles are cut into work items.  By default whole tiles for the full waves and, when
 // the last wave is partly filled, its tiles cut into the number of slices (2 or 4) that lets the
-// clusters finish it soonest; slices run a little below a whole tile's rate (more operand traffic
+// clusters finish it soonest; slices run well below a whole tile's rate (more operand traffic
 // per flop), which the estimate charges.  SILE_CUDA_GEMM_AG_SPLIT = off | s1,s2,n1 overrides it
 // (tuning): the first n1 tiles in 2^s1 slices, the others in 2^s2; n1 < 0 = the full waves.
+// The cut of the last, partly filled wave (log2 of the slices per tile) and the time that wave
+// then takes, in whole-tile times.  Measured on 8192 x N x 8192: a half slice runs at 0.7 and a
+// quarter slice at 0.4 of a whole tile's rate (A is fetched again for every slice).
+int ag_tail_cut(int rest, int clusters, double* tail_time) {
+  const double cost[3] = {1.0, 1.4, 2.5};
+  int cut = 0;
+  double best = rest > 0 ? 1.0 : 0.0;
+  for (int s = 1; s <= 2 && rest > 0; ++s) {
+    const int waves = ((rest << s) + clusters - 1) / clusters;
+    const double t = cost[s] * waves / (1 << s);
+    if (t < best - 0.05) { best = t; cut = s; }
+  }
+  if (tail_time) *tail_time = best;
+  return cut;
+}
+
+// Whole-tile times the sliced kernel needs for `tiles` 256 x 256 tiles on `clusters` CTA pairs.
+double ag_waves(int64_t tiles, int clusters) {
+  clusters = std::max(clusters, 1);
+  double tail = 0.0;
+  ag_tail_cut(static_cast<int>(tiles % clusters), clusters, &tail);
+  return static_cast<double>(tiles / clusters) + tail;
+}
+
 AgPlan make_ag_plan(int tiles, int clusters, bool bf16) {
   AgPlan plan{};
   plan.idesc[0] = make_idesc_f16(kPairBM, kBN, bf16, false, false);
@@ -1324,14 +1354,9 @@ AgPlan make_ag_plan(int tiles, int clusters, bool bf16) {
   const int full = tiles / clusters * clusters;  // tiles in completely filled waves
   const int rest = tiles - full;
   int n1 = tiles, s1 = 0, s2 = 0;
-  if (rest > 0) {
-    const double cost[3] = {1.0, 1.08, 1.3};
-    double best = 1.0;
-    for (int s = 1; s <= 2; ++s) {
-      const int waves = ((rest << s) + clusters - 1) / clusters;
-      const double t = cost[s] * waves / (1 << s);
-      if (t < best - 0.05) { best = t; n1 = full; s2 = s; }
-    }
+  if (const int cut = ag_tail_cut(rest, clusters, nullptr)) {
+    n1 = full;
+    s2 = cut;
   }
   if (const char* e = getenv("SILE_CUDA_GEMM_AG_SPLIT")) {
     int a = 0, b = 0, c = -1;
@@ -1348,7 +1373,7 @@ AgPlan make_ag_plan(int tiles, int clusters, bool bf16) {
 }
 
 template <typename OutT>
-int launch_pair_ag(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& gp, bool bf16, int vec_ok, int* status,
+int launch_pair_ag(const CUtensorMap& ta, const AgBMaps& tb, const GemmParams& gp, bool bf16, int vec_ok, int* status,
                    cudaStream_t stream, const PeerOut& peers, const OutMaps& out_maps) {
   const int m_blocks = (gp.m_valid + kPairBM - 1) / kPairBM;
   const int tiles = m_blocks * gp.n_blocks;
@@ -1366,8 +1391,8 @@ int launch_pair_ag(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParam
   cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, &gemm_tn_pair_ag_kernel<OutT>, ta, tb, gp, plan, vec_ok, status, peers, out_maps));
-  note_kernel(sizeof(OutT) == 4 ? "gemm_tn_pair_ag_kernel<float>" : "gemm_tn_pair_ag_kernel<16-bit>", cfg.gridDim.x, cfg.blockDim.x,
+  SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, &gemm_tn_pair_sliced_kernel<OutT>, ta, tb, gp, plan, vec_ok, status, peers, out_maps));
+  note_kernel(sizeof(OutT) == 4 ? "gemm_tn_pair_sliced_kernel<float>" : "gemm_tn_pair_sliced_kernel<16-bit>", cfg.gridDim.x, cfg.blockDim.x,
               cfg.dynamicSmemBytes);
   return SILE_OK;
 }
@@ -1475,8 +1500,22 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
   // Fused GEMM + all-gather: the 256 x 256 pair kernel whose epilogue stages whole tiles and lets
   // the stores to every destination drain under the following tiles (16-bit outputs); the wide
   // kernel otherwise, or when asked for.
+  // One GPU: the sliced kernel instead of the wide one when its 256 x 256 tiles fill the CTA pairs'
+  // waves better (8192 x 4096 x 8192: 6.9 waves against 3.46 -> 4 of the wide tiles, 0.333 ms
+  // against 0.366); per flop in a full wave the wide kernel is 3 % ahead.
+  bool prefer_sliced = false;
+  if (forced == 0 && p.num_peers == 0 && use_wide) {
+    const int clusters = p.out_dtype == SILE_DTYPE_F32    ? ag_max_clusters<float>()
+                         : p.out_dtype == SILE_DTYPE_BF16 ? ag_max_clusters<__nv_bfloat16>()
+                                                          : ag_max_clusters<__half>();
+    const int wide_clusters = pair_max_clusters_for<true>(p.out_dtype);
+    if (clusters > 0 && wide_clusters > 0) {
+      const double wide_time = 2.0 * static_cast<double>((tiles_wide + wide_clusters - 1) / wide_clusters) / 1.03;
+      prefer_sliced = ag_waves(tiles_pair, clusters) < 0.96 * wide_time;
+    }
+  }
   bool use_ag = false;
-  if (e.m_valid > kBM && ((p.num_peers > 0 && forced_ag_kernel() != 1) || (p.num_peers == 0 && forced == 4))) {
+  if (e.m_valid > kBM && ((p.num_peers > 0 && forced_ag_kernel() != 1) || (p.num_peers == 0 && (forced == 4 || prefer_sliced)))) {
     use_ag = (p.out_dtype == SILE_DTYPE_F32    ? ag_max_clusters<float>()
               : p.out_dtype == SILE_DTYPE_BF16 ? ag_max_clusters<__nv_bfloat16>()
                                                : ag_max_clusters<__half>()) > 0;
@@ -1484,7 +1523,9 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
   }
   use_pair = use_pair || use_wide || use_ag;
   const uint32_t box_a[2] = {kBK, kBM};
-  const uint32_t box_b[2] = {kBK, use_ag ? static_cast<uint32_t>(kAgBBoxRows) : use_pair ? 128u : static_cast<uint32_t>(kBN)};
+  const uint32_t box_b[2] = {kBK, use_pair ? 128u : static_cast<uint32_t>(kBN)};
+  static const AgBMaps zero_b_maps{};
+  AgBMaps tb_ag = zero_b_maps;  // the sliced kernel's three maps of B
 
   if (p.in_dtype == SILE_DTYPE_F32) {
     if (e.k_eff == 0) {
@@ -1518,6 +1559,10 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
     const uint64_t stride[1] = {static_cast<uint64_t>(e.kp) * 2};
     if (int rc = encode_tensor_map(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_hi, dims_a, stride, box_a, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
     if (int rc = encode_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_hi, dims_b, stride, box_b, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+    for (int s = 0; use_ag && s < 3; ++s) {
+      const uint32_t box[2] = {kBK, 128u >> s};
+      if (int rc = encode_tensor_map(&tb_ag.map[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_hi, dims_b, stride, box, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+    }
     gp.num_segs = 3;
     gp.k_blocks_per_seg = static_cast<int>(e.kp / kBK);
     // small terms first: lo*hi, hi*lo, then hi*hi
@@ -1549,6 +1594,10 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
     const uint64_t stride_b[1] = {b_ld * 2};
     if (int rc = encode_tensor_map(&ta, dt, 2, p.a, dims_a, stride_a, box_a, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
     if (int rc = encode_tensor_map(&tb, dt, 2, b_kmajor, dims_b, stride_b, box_b, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+    for (int s = 0; use_ag && s < 3; ++s) {
+      const uint32_t box[2] = {kBK, 128u >> s};
+      if (int rc = encode_tensor_map(&tb_ag.map[s], dt, 2, b_kmajor, dims_b, stride_b, box, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+    }
     gp.num_segs = 1;
     gp.k_blocks_per_seg = static_cast<int>((e.k_eff + kBK - 1) / kBK);
   }
@@ -1584,9 +1633,9 @@ int gemm_launch(const GemmProblem& p, cudaStream_t stream) {
         if (int rc = encode_tensor_map(&maps.map[i], odt, 2, peers.ptr[i], odims, ostride, obox, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
     }
     if (use_ag) {
-      if (p.out_dtype == SILE_DTYPE_F32) return launch_pair_ag<float>(ta, tb, gp, bf16, vec_ok, status, stream, peers, maps);
-      if (p.out_dtype == SILE_DTYPE_BF16) return launch_pair_ag<__nv_bfloat16>(ta, tb, gp, bf16, vec_ok, status, stream, peers, maps);
-      return launch_pair_ag<__half>(ta, tb, gp, bf16, vec_ok, status, stream, peers, maps);
+      if (p.out_dtype == SILE_DTYPE_F32) return launch_pair_ag<float>(ta, tb_ag, gp, bf16, vec_ok, status, stream, peers, maps);
+      if (p.out_dtype == SILE_DTYPE_BF16) return launch_pair_ag<__nv_bfloat16>(ta, tb_ag, gp, bf16, vec_ok, status, stream, peers, maps);
+      return launch_pair_ag<__half>(ta, tb_ag, gp, bf16, vec_ok, status, stream, peers, maps);
     }
     return launch_pair<true>(p.out_dtype, ta, tb, p.c, gp, idesc2, vec_ok, status, stream, peers, &maps);
   }

@@ -235,7 +235,7 @@ def test_fused_allgather_epilogue_on_one_gpu(sb, oracle, monkeypatch, world, m, 
     for rank in range(world):
         sb.matmul_allgather(da, db[rank * w:(rank + 1) * w].contiguous(), ptrs, rank, n, torch.bfloat16)
     chosen = sb._lib.lib().sile_cuda_last_kernel().decode()
-    assert chosen.startswith("gemm_tn_pair_ag_kernel" if ag_kernel == "pair" else "gemm_tn_pair_wide_kernel"), chosen
+    assert chosen.startswith("gemm_tn_pair_sliced_kernel" if ag_kernel == "pair" else "gemm_tn_pair_wide_kernel"), chosen
     sb.synchronize()
     want = oracle.matmul(a_up, b_up, 1, 1, 1)
     for b in bufs:
@@ -261,7 +261,7 @@ def test_fused_allgather_epilogue_with_f32_outputs(sb, oracle, monkeypatch, ag_k
     for rank in range(world):
         sb.matmul_allgather(da, db[rank * w:(rank + 1) * w].contiguous(), [b.data_ptr() for b in bufs], rank, n, torch.float32)
     chosen = sb._lib.lib().sile_cuda_last_kernel().decode()
-    assert chosen.startswith("gemm_tn_pair_ag_kernel<float>" if ag_kernel == "pair" else "gemm_tn_pair_wide_kernel"), chosen
+    assert chosen.startswith("gemm_tn_pair_sliced_kernel<float>" if ag_kernel == "pair" else "gemm_tn_pair_wide_kernel"), chosen
     sb.synchronize()
     assert rel_err(bufs[0].cpu().numpy(), oracle.matmul(a_up, b_up, 1, 1, 1)) < 1e-5
     assert torch.equal(bufs[0], bufs[1])
