@@ -518,11 +518,12 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 // With a single destination it is also the fastest kernel for shapes whose 256 x 512 tiles fill
 // the CTA pairs' waves badly (gemm_launch compares the two).
 //
-// Work items are tiles or column slices of tiles.  The first `n1` tiles are cut into 2^s1 slices
-// of 256 >> s1 columns, the others into 2^s2 (s = 0, 1 or 2): a slice is an MMA of that N fed by
+// Work items are tiles or column slices of tiles, in three groups -- head, body, tail -- each cut
+// into 2^s slices of 256 >> s columns (s = 0, 1 or 2): a slice is an MMA of that N fed by
 // (128 >> s) rows of B per CTA and stored as (4 >> s) boxes.  Slicing the tiles of the last,
 // partly filled wave halves the time that wave takes (256 tiles on 74 CTA pairs are 3.5 waves
-// instead of 4), and slices finish -- and start crossing NVLink -- sooner than whole tiles.
+// instead of 4); a sliced head finishes -- and starts crossing NVLink -- sooner than whole tiles,
+// which pays when the exchange bounds the step.
 constexpr int kAgStages = 6;
 constexpr int kAgStagingBytes = 4 * 2 * 4096;  // 4 epilogue warps x 2 boxes of 32 rows x 128 bytes
 constexpr int kAgSmemBytes = kAgStages * kPairStageBytes + kAgStagingBytes + 256 + 1024;
@@ -535,24 +536,27 @@ struct AgBMaps {
 };
 
 struct AgPlan {
-  int n1;             // tiles in the first group
-  int s1, s2;         // log2 of the slices per tile in the first / second group
-  int items;          // (n1 << s1) + ((tiles - n1) << s2)
+  int n[2];           // tiles in the head and in the body; the tail takes the rest
+  int s[3];           // log2 of the slices per tile in head / body / tail
+  int items;          // (n[0] << s[0]) + (n[1] << s[1]) + ((tiles - n[0] - n[1]) << s[2])
   uint32_t idesc[3];  // instruction descriptors for N = 256, 128, 64
 };
 
 __device__ __forceinline__ void ag_item(int i, const AgPlan& plan, int& tile, int& part, int& s) {
-  const int g1 = plan.n1 << plan.s1;
-  if (i < g1) {
-    s = plan.s1;
-    tile = i >> s;
-    part = i - (tile << s);
-  } else {
-    const int j = i - g1;
-    s = plan.s2;
-    tile = plan.n1 + (j >> s);
-    part = j - ((j >> s) << s);
+  int first = 0;  // first tile of the group item i falls in
+  s = plan.s[0];
+  if (i >= (plan.n[0] << plan.s[0])) {
+    i -= plan.n[0] << plan.s[0];
+    first = plan.n[0];
+    s = plan.s[1];
+    if (i >= (plan.n[1] << plan.s[1])) {
+      i -= plan.n[1] << plan.s[1];
+      first += plan.n[1];
+      s = plan.s[2];
+    }
   }
+  tile = first + (i >> s);
+  part = i - ((i >> s) << s);
 }
 
 template <typename OutT>
@@ -1316,11 +1320,6 @@ int ag_max_clusters() {
   return max_clusters = n;
 }
 
-// How the tiles are cut into work items.  By default whole tiles for the full waves and, when
-// the last wave is partly filled, its tiles cut into the number of slices (2 or 4) that lets the
-// clusters finish it soonest; slices run well below a whole tile's rate (more operand traffic
-// per flop), which the estimate charges.  SILE_CUDA_GEMM_AG_SPLIT = off | s1,s2,n1 overrides it
-// (tuning): the first n1 tiles in 2^s1 slices, the others in 2^s2; n1 < 0 = the full waves.
 // The cut of the last, partly filled wave (log2 of the slices per tile) and the time that wave
 // then takes, in whole-tile times.  Measured on 8192 x N x 8192: a half slice runs at 0.7 and a
 // quarter slice at 0.4 of a whole tile's rate (A is fetched again for every slice).
@@ -1345,30 +1344,42 @@ double ag_waves(int64_t tiles, int clusters) {
   return static_cast<double>(tiles / clusters) + tail;
 }
 
-AgPlan make_ag_plan(int tiles, int clusters, bool bf16) {
+// How the tiles are cut into work items.  Body: whole tiles.  Tail: when the last wave is partly
+// filled, its tiles cut into the number of slices (2 or 4) that lets the clusters finish it
+// soonest; slices run well below a whole tile's rate (more operand traffic per flop), which the
+// estimate charges.  Head: with `exchange_bound` (the peers' share of the output takes longer to
+// cross NVLink than the tiles take to compute) the first half wave of tiles is cut in two, so the
+// first stores leave after 0.7 of a tile time instead of a whole one.
+// SILE_CUDA_GEMM_AG_SPLIT = off | s0,n0,s1,n1,s2 overrides it (tuning, tests): the first n0 tiles
+// in 2^s0 slices, the next n1 in 2^s1 (n1 < 0: up to the last full wave), the rest in 2^s2.
+AgPlan make_ag_plan(int tiles, int clusters, bool bf16, bool exchange_bound) {
   AgPlan plan{};
   plan.idesc[0] = make_idesc_f16(kPairBM, kBN, bf16, false, false);
   plan.idesc[1] = make_idesc_f16(kPairBM, kBN / 2, bf16, false, false);
   plan.idesc[2] = make_idesc_f16(kPairBM, kBN / 4, bf16, false, false);
   clusters = std::max(clusters, 1);
-  const int full = tiles / clusters * clusters;  // tiles in completely filled waves
-  const int rest = tiles - full;
-  int n1 = tiles, s1 = 0, s2 = 0;
-  if (const int cut = ag_tail_cut(rest, clusters, nullptr)) {
-    n1 = full;
-    s2 = cut;
+  int n0 = 0, s0 = 0, s1 = 0, s2 = 0;
+  if (exchange_bound && tiles > clusters) {
+    n0 = clusters / 2;
+    s0 = 1;
   }
+  auto body_of = [&](int head) { return (tiles - head) / clusters * clusters; };  // tiles in filled waves
+  int n1 = body_of(n0);
+  s2 = ag_tail_cut(tiles - n0 - n1, clusters, nullptr);
   if (const char* e = getenv("SILE_CUDA_GEMM_AG_SPLIT")) {
-    int a = 0, b = 0, c = -1;
+    int v[5] = {0, 0, 0, -1, 0};
     if (!strcmp(e, "off")) {
-      n1 = tiles; s1 = 0; s2 = 0;
-    } else if (sscanf(e, "%d,%d,%d", &a, &b, &c) >= 2 && a >= 0 && a <= 2 && b >= 0 && b <= 2) {
-      s1 = a; s2 = b;
-      n1 = (c < 0 || c > tiles) ? full : c;
+      n0 = 0; s0 = 0; s1 = 0; n1 = tiles; s2 = 0;
+    } else if (sscanf(e, "%d,%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3], &v[4]) == 5 && v[0] >= 0 && v[0] <= 2 && v[2] >= 0 &&
+               v[2] <= 2 && v[4] >= 0 && v[4] <= 2 && v[1] >= 0) {
+      s0 = v[0]; n0 = std::min(v[1], tiles);
+      s1 = v[2]; n1 = (v[3] < 0 || v[3] > tiles - n0) ? body_of(n0) : v[3];
+      s2 = v[4];
     }
   }
-  plan.n1 = n1; plan.s1 = s1; plan.s2 = s2;
-  plan.items = (n1 << s1) + ((tiles - n1) << s2);
+  plan.n[0] = n0; plan.n[1] = n1;
+  plan.s[0] = s0; plan.s[1] = s1; plan.s[2] = s2;
+  plan.items = (n0 << s0) + (n1 << s1) + ((tiles - n0 - n1) << s2);
   return plan;
 }
 
@@ -1378,7 +1389,13 @@ int launch_pair_ag(const CUtensorMap& ta, const AgBMaps& tb, const GemmParams& g
   const int m_blocks = (gp.m_valid + kPairBM - 1) / kPairBM;
   const int tiles = m_blocks * gp.n_blocks;
   const int max_clusters = ag_max_clusters<OutT>();
-  const AgPlan plan = make_ag_plan(tiles, max_clusters, bf16);
+  // Exchange against compute, at the rates measured for this kernel on 8192^3 over 4 and 8 GPUs:
+  // 0.58 TB/s of peer stores leaving a GPU, 1.4 PFLOP/s of tensor work.
+  const double k_total = static_cast<double>(gp.k_blocks_per_seg) * gp.num_segs * kBK;
+  const double out_elems = static_cast<double>(gp.m_valid) * gp.n_valid;
+  const double link_s = out_elems * sizeof(OutT) * (peers.count - 1) / 0.58e12;
+  const double math_s = 2.0 * out_elems * k_total / 1.4e15;
+  const AgPlan plan = make_ag_plan(tiles, max_clusters, bf16, peers.count > 1 && link_s > math_s);
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
