@@ -1348,8 +1348,10 @@ double ag_waves(int64_t tiles, int clusters) {
 // filled, its tiles cut into the number of slices (2 or 4) that lets the clusters finish it
 // soonest; slices run well below a whole tile's rate (more operand traffic per flop), which the
 // estimate charges.  Head: with `exchange_bound` (the peers' share of the output takes longer to
-// cross NVLink than the tiles take to compute) the first half wave of tiles is cut in two, so the
-// first stores leave after 0.7 of a tile time instead of a whole one.
+// cross NVLink than the tiles take to compute) a quarter wave of tiles is cut in two, so half of
+// the clusters send their first stores after 0.7 of a tile time and the others after a whole one
+// (8192^3 over 8 GPUs: 0.247 ms against 0.256 uncut; cutting a half wave, so that every cluster
+// starts with a half tile, gave 0.258).
 // SILE_CUDA_GEMM_AG_SPLIT = off | s0,n0,s1,n1,s2 overrides it (tuning, tests): the first n0 tiles
 // in 2^s0 slices, the next n1 in 2^s1 (n1 < 0: up to the last full wave), the rest in 2^s2.
 AgPlan make_ag_plan(int tiles, int clusters, bool bf16, bool exchange_bound) {
@@ -1360,7 +1362,7 @@ AgPlan make_ag_plan(int tiles, int clusters, bool bf16, bool exchange_bound) {
   clusters = std::max(clusters, 1);
   int n0 = 0, s0 = 0, s1 = 0, s2 = 0;
   if (exchange_bound && tiles > clusters) {
-    n0 = clusters / 2;
+    n0 = clusters / 4;  // half of the clusters start with a half tile, the others with a whole one
     s0 = 1;
   }
   auto body_of = [&](int head) { return (tiles - head) / clusters * clusters; };  // tiles in filled waves
