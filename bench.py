@@ -512,7 +512,8 @@ def main():
     flops = 2.0 * n ** 3
     value = flops / (ms_step * 1e-3) / 1e12
 
-    gemm_kernel = sb._lib.lib().sile_cuda_last_kernel().decode().split(" ")[0]
+    gemm_launch = sb._lib.lib().sile_cuda_last_kernel().decode()  # kernel, slice plan if any, grid, block, shared memory
+    gemm_kernel = gemm_launch.split(" ")[0]
     gemm_traffic = ncu_traffic("gemm_bf16_8192", sb)[1] if p == 1 else None
 
     # ---- how long the per-step device barrier alone takes (N > 1, fused exchange) -----------------
@@ -852,7 +853,7 @@ def main():
         "bound": "tensor", "achieved": achieved, "peak": peaks[peak_key], "unit": "TFLOP/s",
         "frac": achieved / peaks[peak_key], "traffic": gemm_traffic,
         "peak_source": f"{peak_src} {peak_key}", "frac_of_nominal_dense_bf16": achieved / NOMINAL_BF16_TFLOPS,
-        "kernel": gemm_kernel, "algorithmic_flops_per_launch": per_gpu_flops,
+        "kernel": gemm_kernel, "launch": gemm_launch, "algorithmic_flops_per_launch": per_gpu_flops,
     }
     if p > 1:
         roofline["note"] = ("per-GPU share of the whole step (GEMM with the all-gather of C in its epilogue, then the barrier), "

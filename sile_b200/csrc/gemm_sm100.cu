@@ -30,6 +30,7 @@
 #include <cstring>
 #include <mutex>
 #include <type_traits>
+#include <vector>
 
 #include "internal.h"
 #include "ptx.cuh"
@@ -518,12 +519,12 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 // With a single destination it is also the fastest kernel for shapes whose 256 x 512 tiles fill
 // the CTA pairs' waves badly (gemm_launch compares the two).
 //
-// Work items are tiles or column slices of tiles, in three groups -- head, body, tail -- each cut
-// into 2^s slices of 256 >> s columns (s = 0, 1 or 2): a slice is an MMA of that N fed by
-// (128 >> s) rows of B per CTA and stored as (4 >> s) boxes.  Slicing the tiles of the last,
-// partly filled wave halves the time that wave takes (256 tiles on 74 CTA pairs are 3.5 waves
-// instead of 4); a sliced head finishes -- and starts crossing NVLink -- sooner than whole tiles,
-// which pays when the exchange bounds the step.
+// Work items are tiles or column slices of tiles, in consecutive groups each cut into 2^s slices
+// of 256 >> s columns (s = 0, 1 or 2): a slice is an MMA of that N fed by (128 >> s) rows of B per
+// CTA and stored as (4 >> s) boxes.  Item i goes to CTA pair i mod (pairs).  Slicing the tiles of
+// the last, partly filled wave halves the time that wave takes (256 tiles on 74 CTA pairs are 3.5
+// waves instead of 4); with several destinations a few sliced tiles at the head put the CTA
+// pairs out of step with one another, so that their store bursts do not all hit NVLink at once.
 constexpr int kAgStages = 6;
 constexpr int kAgStagingBytes = 4 * 2 * 4096;  // 4 epilogue warps x 2 boxes of 32 rows x 128 bytes
 constexpr int kAgSmemBytes = kAgStages * kPairStageBytes + kAgStagingBytes + 256 + 1024;
@@ -535,26 +536,23 @@ struct AgBMaps {
   CUtensorMap map[3];
 };
 
+constexpr int kAgMaxGroups = 6;
 struct AgPlan {
-  int n[2];           // tiles in the head and in the body; the tail takes the rest
-  int s[3];           // log2 of the slices per tile in head / body / tail
-  int items;          // (n[0] << s[0]) + (n[1] << s[1]) + ((tiles - n[0] - n[1]) << s[2])
-  uint32_t idesc[3];  // instruction descriptors for N = 256, 128, 64
+  int groups;               // consecutive groups of tiles, each cut its own way
+  int n[kAgMaxGroups];      // tiles per group (the last group takes what is left)
+  int s[kAgMaxGroups];      // log2 of the slices per tile
+  int items;                // sum of n[g] << s[g]
+  uint32_t idesc[3];        // instruction descriptors for N = 256, 128, 64
 };
 
 __device__ __forceinline__ void ag_item(int i, const AgPlan& plan, int& tile, int& part, int& s) {
-  int first = 0;  // first tile of the group item i falls in
-  s = plan.s[0];
-  if (i >= (plan.n[0] << plan.s[0])) {
-    i -= plan.n[0] << plan.s[0];
-    first = plan.n[0];
-    s = plan.s[1];
-    if (i >= (plan.n[1] << plan.s[1])) {
-      i -= plan.n[1] << plan.s[1];
-      first += plan.n[1];
-      s = plan.s[2];
-    }
+  int first = 0, g = 0;  // first tile of the group item i falls in
+  while (g + 1 < plan.groups && i >= (plan.n[g] << plan.s[g])) {
+    i -= plan.n[g] << plan.s[g];
+    first += plan.n[g];
+    ++g;
   }
+  s = plan.s[g];
   tile = first + (i >> s);
   part = i - ((i >> s) << s);
 }
@@ -1344,44 +1342,90 @@ double ag_waves(int64_t tiles, int clusters) {
   return static_cast<double>(tiles / clusters) + tail;
 }
 
+// Whole-tile times until the busiest CTA pair has finished its items of `plan` (item i runs on
+// pair i mod clusters; a half slice costs 0.7 and a quarter 0.625 of a whole tile).
+double ag_makespan(const AgPlan& plan, int clusters) {
+  const double cost[3] = {1.0, 0.7, 0.625};
+  clusters = std::max(clusters, 1);
+  std::vector<double> busy(static_cast<size_t>(clusters), 0.0);
+  int item = 0;
+  for (int g = 0; g < plan.groups; ++g)
+    for (int i = 0; i < (plan.n[g] << plan.s[g]); ++i, ++item) busy[static_cast<size_t>(item % clusters)] += cost[plan.s[g]];
+  return *std::max_element(busy.begin(), busy.end());
+}
+
 // How the tiles are cut into work items.  Body: whole tiles.  Tail: when the last wave is partly
 // filled, its tiles cut into the number of slices (2 or 4) that lets the clusters finish it
 // soonest; slices run well below a whole tile's rate (more operand traffic per flop), which the
-// estimate charges.  Head: with `exchange_bound` (the peers' share of the output takes longer to
-// cross NVLink than the tiles take to compute) a quarter wave of tiles is cut in two, so half of
-// the clusters send their first stores after 0.7 of a tile time and the others after a whole one
-// (8192^3 over 8 GPUs: 0.247 ms against 0.256 uncut; cutting a half wave, so that every cluster
-// starts with a half tile, gave 0.258).
-// SILE_CUDA_GEMM_AG_SPLIT = off | s0,n0,s1,n1,s2 overrides it (tuning, tests): the first n0 tiles
-// in 2^s0 slices, the next n1 in 2^s1 (n1 < 0: up to the last full wave), the rest in 2^s2.
-AgPlan make_ag_plan(int tiles, int clusters, bool bf16, bool exchange_bound) {
+// estimate charges.  Head, with `stagger` (several destinations): a quarter wave of tiles cut in
+// two, so half of the CTA pairs finish their first item after 0.7 of a tile time and stay 0.3 of a
+// tile time ahead of the others; the waves' store bursts then reach NVLink in two halves
+// (8192^3: 0.240 ms against 0.264 over 4 GPUs, 0.247 against 0.256 over 8; cutting a half wave,
+// which leaves all pairs in step, was slower than no cut at all).
+// SILE_CUDA_GEMM_AG_SPLIT = off | s0,n0,s1,n1,...,s_last overrides it (tuning, tests): n0 tiles
+// in 2^s0 slices, the next n1 in 2^s1, ..., the rest in 2^s_last; a negative n = the whole waves
+// of what is left.
+AgPlan make_ag_plan(int tiles, int clusters, bool bf16, bool stagger, bool exchange_bound) {
   AgPlan plan{};
   plan.idesc[0] = make_idesc_f16(kPairBM, kBN, bf16, false, false);
   plan.idesc[1] = make_idesc_f16(kPairBM, kBN / 2, bf16, false, false);
   plan.idesc[2] = make_idesc_f16(kPairBM, kBN / 4, bf16, false, false);
   clusters = std::max(clusters, 1);
-  int n0 = 0, s0 = 0, s1 = 0, s2 = 0;
-  if (exchange_bound && tiles > clusters) {
-    n0 = clusters / 4;  // half of the clusters start with a half tile, the others with a whole one
-    s0 = 1;
-  }
-  auto body_of = [&](int head) { return (tiles - head) / clusters * clusters; };  // tiles in filled waves
-  int n1 = body_of(n0);
-  s2 = ag_tail_cut(tiles - n0 - n1, clusters, nullptr);
+  auto whole_waves = [&](int left) { return left / clusters * clusters; };
+  int g = 0, left = tiles;
+  auto add = [&](int n, int s) {
+    n = std::min(std::max(n, 0), left);
+    plan.n[g] = n; plan.s[g] = s;
+    left -= n;
+    ++g;
+  };
+  bool from_env = false;
   if (const char* e = getenv("SILE_CUDA_GEMM_AG_SPLIT")) {
-    int v[5] = {0, 0, 0, -1, 0};
     if (!strcmp(e, "off")) {
-      n0 = 0; s0 = 0; s1 = 0; n1 = tiles; s2 = 0;
-    } else if (sscanf(e, "%d,%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3], &v[4]) == 5 && v[0] >= 0 && v[0] <= 2 && v[2] >= 0 &&
-               v[2] <= 2 && v[4] >= 0 && v[4] <= 2 && v[1] >= 0) {
-      s0 = v[0]; n0 = std::min(v[1], tiles);
-      s1 = v[2]; n1 = (v[3] < 0 || v[3] > tiles - n0) ? body_of(n0) : v[3];
-      s2 = v[4];
+      add(tiles, 0);
+      from_env = true;
+    } else {
+      long v[2 * kAgMaxGroups - 1];
+      int count = 0;
+      const char* c = e;
+      while (count < 2 * kAgMaxGroups - 1) {
+        char* end = nullptr;
+        v[count] = strtol(c, &end, 10);
+        if (end == c) break;
+        ++count;
+        if (*end != ',') break;
+        c = end + 1;
+      }
+      bool ok = count % 2 == 1;
+      for (int i = 0; ok && i < count; i += 2) ok = v[i] >= 0 && v[i] <= 2;
+      if (ok) {
+        for (int i = 0; i + 1 < count; i += 2) add(v[i + 1] < 0 ? whole_waves(left) : static_cast<int>(v[i + 1]), static_cast<int>(v[i]));
+        add(left, static_cast<int>(v[count - 1]));
+        from_env = true;
+      }
     }
   }
-  plan.n[0] = n0; plan.n[1] = n1;
-  plan.s[0] = s0; plan.s[1] = s1; plan.s[2] = s2;
-  plan.items = (n0 << s0) + (n1 << s1) + ((tiles - n0 - n1) << s2);
+  if (!from_env) {
+    if (stagger && tiles > clusters) add(clusters / 4, 1);
+    add(whole_waves(left), 0);
+    // The tail's cut: the one with which the busiest pair finishes soonest (the head may have
+    // shifted the tail off a wave boundary); when the exchange bounds the step, as fine as one
+    // wave allows, for smaller last stores.
+    int cut = ag_tail_cut(left, clusters, nullptr);
+    if (!exchange_bound && left > 0) {
+      double best = 0.0;
+      for (int c = 0; c <= 2; ++c) {
+        AgPlan trial = plan;
+        trial.n[g] = left; trial.s[g] = c; trial.groups = g + 1;
+        const double t = ag_makespan(trial, clusters);
+        if (c == 0 || t < best - 0.01) { best = t; cut = c; }
+      }
+    }
+    add(left, cut);
+  }
+  plan.groups = g;
+  plan.items = 0;
+  for (int i = 0; i < g; ++i) plan.items += plan.n[i] << plan.s[i];
   return plan;
 }
 
@@ -1391,13 +1435,19 @@ int launch_pair_ag(const CUtensorMap& ta, const AgBMaps& tb, const GemmParams& g
   const int m_blocks = (gp.m_valid + kPairBM - 1) / kPairBM;
   const int tiles = m_blocks * gp.n_blocks;
   const int max_clusters = ag_max_clusters<OutT>();
-  // Exchange against compute, at the rates measured for this kernel on 8192^3 over 4 and 8 GPUs:
-  // 0.58 TB/s of peer stores leaving a GPU, 1.4 PFLOP/s of tensor work.
-  const double k_total = static_cast<double>(gp.k_blocks_per_seg) * gp.num_segs * kBK;
-  const double out_elems = static_cast<double>(gp.m_valid) * gp.n_valid;
-  const double link_s = out_elems * sizeof(OutT) * (peers.count - 1) / 0.58e12;
-  const double math_s = 2.0 * out_elems * k_total / 1.4e15;
-  const AgPlan plan = make_ag_plan(tiles, max_clusters, bf16, peers.count > 1 && link_s > math_s);
+  // Several destinations: the staggered head, unless it makes the busiest CTA pair finish later
+  // and the exchange is not what bounds the step anyway (rates measured for this kernel on 8192^3
+  // over 4 and 8 GPUs: 0.58 TB/s of peer stores leaving a GPU, 1.4 PFLOP/s of tensor work).
+  AgPlan plan = make_ag_plan(tiles, max_clusters, bf16, false, false);
+  if (peers.count > 1) {
+    const double k_total = static_cast<double>(gp.k_blocks_per_seg) * gp.num_segs * kBK;
+    const double out_elems = static_cast<double>(gp.m_valid) * gp.n_valid;
+    const double link_s = out_elems * sizeof(OutT) * (peers.count - 1) / 0.58e12;
+    const double math_s = 2.0 * out_elems * k_total / 1.4e15;
+    const bool exchange_bound = link_s > math_s;
+    const AgPlan staggered = make_ag_plan(tiles, max_clusters, bf16, true, exchange_bound);
+    if (exchange_bound || ag_makespan(staggered, max_clusters) <= 1.01 * ag_makespan(plan, max_clusters)) plan = staggered;
+  }
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1411,8 +1461,12 @@ int launch_pair_ag(const CUtensorMap& ta, const AgBMaps& tb, const GemmParams& g
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, &gemm_tn_pair_sliced_kernel<OutT>, ta, tb, gp, plan, vec_ok, status, peers, out_maps));
-  note_kernel(sizeof(OutT) == 4 ? "gemm_tn_pair_sliced_kernel<float>" : "gemm_tn_pair_sliced_kernel<16-bit>", cfg.gridDim.x, cfg.blockDim.x,
-              cfg.dynamicSmemBytes);
+  // name, then the plan: tiles x slices per group, e.g. "plan=18x2+222x1+16x2"
+  char name[160];
+  int len = snprintf(name, sizeof(name), "%s plan=", sizeof(OutT) == 4 ? "gemm_tn_pair_sliced_kernel<float>" : "gemm_tn_pair_sliced_kernel<16-bit>");
+  for (int g = 0; g < plan.groups && len < static_cast<int>(sizeof(name)) - 16; ++g)
+    len += snprintf(name + len, sizeof(name) - len, "%s%dx%d", g ? "+" : "", plan.n[g], 1 << plan.s[g]);
+  note_kernel(name, cfg.gridDim.x, cfg.blockDim.x, cfg.dynamicSmemBytes);
   return SILE_OK;
 }
 

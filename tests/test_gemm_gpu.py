@@ -207,7 +207,7 @@ def test_g3_bf16_8192_sampled_tiles_and_linearity(sb, oracle):
     assert torch.equal(dc2, dc * 2)
 
 
-@pytest.mark.parametrize("ag_kernel", ["pair", "pair:off", "pair:1,1,0,2,2", "pair:2,1,1,1,0", "pair:0,0,1,-1,2", "wide"])
+@pytest.mark.parametrize("ag_kernel", ["pair", "pair:off", "pair:1,1,0,2,2", "pair:2,1,1,1,0", "pair:0,0,1,-1,2", "pair:1,1,0,1,1,1,0", "wide"])
 @pytest.mark.parametrize("world,m", [(2, 512), (4, 512), (8, 1000)])
 def test_fused_allgather_epilogue_on_one_gpu(sb, oracle, monkeypatch, world, m, ag_kernel):
     """The GEMM whose epilogue stores its column block into every rank's buffer, with the ranks
@@ -216,7 +216,7 @@ def test_fused_allgather_epilogue_on_one_gpu(sb, oracle, monkeypatch, world, m, 
     pair kernel (the default) and the wide one -- and a row count that leaves a ragged last tile
     (per-thread stores to every destination).  The pair kernel cuts tiles into column slices;
     the suffix names the cut: the default plan, none, or `s0,n0,s1,n1,s2` = the first n0 tiles in
-    2^s0 slices, the next n1 in 2^s1, the others in 2^s2."""
+    2^s0 slices, the next n1 in 2^s1, ..., the others in 2^s_last."""
     import torch
     ag_kernel, _, split = ag_kernel.partition(":")
     if split:
