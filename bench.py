@@ -63,6 +63,9 @@ SIDE_WORKLOADS = {
     "attn_fwd_h32_s8192_d128_causal_one_gpu_shard": (32, 8192, True),
     "attn_fwd_b8_h32_s8192_d128_causal": (256, 8192, True),
     "gemm_f32_4096": None,
+    # one rank's column block of the headline GEMM at 2 / 4 GPUs, on one GPU (no exchange)
+    "gemm_bf16_8192_shard_of_2": ("shard", 4096),
+    "gemm_bf16_8192_shard_of_4": ("shard", 2048),
     "tileops_hbm": "tileops",
 }
 
@@ -326,6 +329,15 @@ def run_side_workload(name, iters, warmup, peaks):
         ms = timed(sb.matmul(af, bf, cf, 64, 64, 32).apply)
         return {"ms": ms, "tflops_f32_equivalent": 2.0 * 4096 ** 3 / (ms * 1e-3) / 1e12,
                 "note": "3 bf16 tensor-core passes (hi*hi + hi*lo + lo*hi), f32 accumulate"}
+    if spec[0] == "shard":
+        n, ns = GEMM_N, spec[1]
+        a = (torch.randn(n, n, generator=g, device=dev) / n ** 0.5).to(torch.bfloat16)
+        b = (torch.randn(ns, n, generator=g, device=dev) / n ** 0.5).to(torch.bfloat16)   # [N/p, K]: column-major block
+        c = torch.zeros(n, ns, device=dev, dtype=torch.bfloat16)
+        ms = timed(sb.matmul(a, b, c, *ORACLE_TILE, b_layout=sb._lib.LAYOUT_COL_MAJOR).apply)
+        tf = 2.0 * n * ns * n / (ms * 1e-3) / 1e12
+        return {"ms": ms, "tflops": tf, "frac_of_measured_gemm_peak": tf / peaks["bf16_tflops"],
+                "launch": sb._lib.lib().sile_cuda_last_kernel().decode()}
     bh, s, causal = spec
     q, k, v = [torch.randn(bh, s, 128, generator=g, device=dev).to(torch.bfloat16) for _ in range(3)]
     o = torch.zeros_like(q)
@@ -676,6 +688,8 @@ def main():
 
     if p == 1 and not args.no_extras:
         for name in SIDE_WORKLOADS:
+            if "shard_of" in name:
+                continue  # profiling helpers (one rank's block of the multi-GPU GEMM on one GPU)
             extras[name] = run_side_workload(name, 10 if "b8" in name else 20, 3, peaks)
         # the configuration the attention target is stated on, batch 8 x 32 heads x 8192 causal,
         # kept whole on this GPU: device-resident rate, roofline, parity, end to end, CPU baseline
