@@ -166,7 +166,8 @@ int sile_cuda_launch_host(const SileKernelDesc* desc, void* const* host_buffers,
  * C[:, n_begin : n_begin+n_count] = A * B[:, n_begin : n_begin+n_count].
  * `b_shard` is that block of a column-major B ([n_count, K] contiguous); `c` is
  * the base of a row-major buffer with `n_total` columns (pass n_total = n_count
- * and n_begin = 0 for a packed shard buffer).  Asynchronous on `stream`. */
+ * and n_begin = 0 for a packed shard buffer).  Asynchronous on `stream`.
+ * SILE_FLAG_ACCUMULATE is refused (SILE_ERR_UNSUPPORTED). */
 int sile_cuda_matmul_shard(const SileKernelDesc* desc, const void* a, const void* b_shard, void* c,
                            int64_t m, int64_t n_total, int64_t k, int64_t n_begin, int64_t n_count,
                            void* stream);
@@ -180,9 +181,9 @@ int sile_cuda_matmul_shard(const SileKernelDesc* desc, const void* a, const void
  * ragged or launch-masked tiles as st.global from the epilogue warps; the kernel waits on no
  * other GPU.  When the call has completed on every rank and the ranks have synchronised (the
  * caller's barrier), each holds the whole C.  16-bit operands, column-major B, N divisible by
- * world, M > 128.  With 16-bit outputs the 256 x 256 CTA-pair kernel built for this epilogue
- * runs (stores drain under the next tile); f32 outputs take the 256 x 512 kernel and need more
- * than 256 columns per rank.  SILE_FLAG_ACCUMULATE is refused here. */
+ * world, M > 128.  The 256 x 256 CTA-pair kernel with sliced tiles built for this epilogue
+ * runs (stores drain under the next tile; 16-bit and f32 outputs).  SILE_FLAG_ACCUMULATE is
+ * refused here. */
 int sile_cuda_matmul_allgather(const SileKernelDesc* desc, const void* a, const void* b_shard,
                                void* const* c_peers, int32_t world, int32_t rank, int64_t m,
                                int64_t n_total, int64_t k, void* stream);

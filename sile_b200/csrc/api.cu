@@ -786,6 +786,7 @@ int sile_cuda_matmul_shard(const SileKernelDesc* desc, const void* a, const void
   if (desc->op != SILE_OP_MATMUL) return fail(SILE_ERR_INVALID, "matmul_shard: description is not a matmul");
   if (!a || !b_shard || !c) return fail(SILE_ERR_INVALID, "null buffer");
   if (n_begin < 0 || n_count <= 0 || n_begin + n_count > n_total) return fail(SILE_ERR_INVALID, "matmul_shard: column block out of range");
+  if (desc->flags & SILE_FLAG_ACCUMULATE) return fail(SILE_ERR_UNSUPPORTED, "matmul_shard: seeded accumulator not supported");
   if (desc->in_dtype == SILE_DTYPE_F32 || desc->b_layout != SILE_LAYOUT_COL_MAJOR)
     return fail(SILE_ERR_UNSUPPORTED, "matmul_shard: 16-bit operands with column-major B only (a column block of B must be contiguous)");
   GemmProblem p;
@@ -807,6 +808,8 @@ int sile_cuda_matmul_allgather(const SileKernelDesc* desc, const void* a, const 
   if (!a || !b_shard || !c_peers) return fail(SILE_ERR_INVALID, "null buffer");
   if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(SILE_ERR_INVALID, "matmul_allgather: bad rank %d of %d (at most 8)", rank, world);
   if (n_total % world != 0) return fail(SILE_ERR_INVALID, "matmul_allgather: N = %lld does not split into %d column blocks", (long long)n_total, world);
+  if (desc->flags & SILE_FLAG_ACCUMULATE)
+    return fail(SILE_ERR_UNSUPPORTED, "matmul_allgather: a seeded accumulator would be read from every rank's buffer; not supported");
   if (desc->in_dtype == SILE_DTYPE_F32 || desc->b_layout != SILE_LAYOUT_COL_MAJOR)
     return fail(SILE_ERR_UNSUPPORTED, "matmul_allgather: 16-bit operands with column-major B only");
   const int64_t n_count = n_total / world, n_begin = n_count * rank;

@@ -267,6 +267,20 @@ def test_fused_allgather_epilogue_with_f32_outputs(sb, oracle, monkeypatch, ag_k
     assert torch.equal(bufs[0], bufs[1])
 
 
+def test_sharded_entry_points_refuse_a_seeded_accumulator(sb):
+    import ctypes as C
+    import torch
+    L = sb._lib
+    a = torch.zeros(256, 64, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(512, 64, device="cuda", dtype=torch.bfloat16)
+    c = torch.zeros(256, 512, device="cuda", dtype=torch.bfloat16)
+    desc = sb.make_desc(L.OP_MATMUL, L.DTYPE_BF16, L.DTYPE_BF16, L.LAYOUT_COL_MAJOR, consts=(1, 1, 1), flags=L.FLAG_ACCUMULATE)
+    ptrs = (C.c_void_p * 1)(c.data_ptr())
+    assert L.lib().sile_cuda_matmul_allgather(C.byref(desc), a.data_ptr(), b.data_ptr(), ptrs, 1, 0, 256, 512, 64, None) == L.ERR_UNSUPPORTED
+    assert L.lib().sile_cuda_matmul_shard(C.byref(desc), a.data_ptr(), b.data_ptr(), c.data_ptr(), 256, 512, 64, 0, 512, None) == L.ERR_UNSUPPORTED
+    assert (c == 0).all()
+
+
 @pytest.mark.parametrize("m", [4096, 4160, 4608])
 def test_host_buffer_launch_pipelines_large_bf16_and_matches_device_launch(sb, m):
     """sile_cuda_launch_host streams a large 16-bit matmul in row chunks (copy in / compute /
