@@ -11,7 +11,7 @@ LIB_DIR = os.path.join(_HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libsile_cuda.so")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 
-SOURCES = ["api.cu", "gemm_sm100.cu", "attn_sm100.cu", "attn_persist_sm100.cu", "attn_pair_sm100.cu", "tileops.cu"]
+SOURCES = ["api.cu", "gemm_sm100.cu", "attn_sm100.cu", "attn_persist_sm100.cu", "attn_split_sm100.cu", "attn_pair_sm100.cu", "tileops.cu"]
 HEADERS = ["internal.h", "ptx.cuh", os.path.join(INCLUDE, "sile_cuda.h")]
 
 NVCC_FLAGS = [

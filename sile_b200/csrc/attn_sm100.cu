@@ -482,6 +482,7 @@ int attention_launch(const AttnProblem& a, cudaStream_t stream) {
   const char* which = std::getenv("SILE_CUDA_ATTN_KERNEL");
   if (which && std::strcmp(which, "pair") == 0 && a.num_peers == 0) return attention_pair_launch(a, stream);
   if (which && std::strcmp(which, "persistent") == 0) return attention_persistent_launch(a, stream);
+  if (which && std::strcmp(which, "split") == 0) return attention_split_launch(a, stream);
 
   int* status = nullptr;
   if (int rc = device_status_word(&status)) return rc;

@@ -114,6 +114,7 @@ int attention_launch(const AttnProblem& p, cudaStream_t stream);
 // CTA-pair kernel and persistent kernel; arguments already validated by attention_launch.
 int attention_pair_launch(const AttnProblem& p, cudaStream_t stream);
 int attention_persistent_launch(const AttnProblem& p, cudaStream_t stream);
+int attention_split_launch(const AttnProblem& a, cudaStream_t stream);
 
 // ---- standalone tile ops (HBM-bound) --------------------------------------------
 int vec_add_launch(const float* a, const float* b, float* c, int64_t n, cudaStream_t stream);

@@ -20,10 +20,11 @@ def sb():
     return sile_b200
 
 
-@pytest.fixture(params=["single", "persistent", "pair"], autouse=True)
+@pytest.fixture(params=["single", "split", "persistent", "pair"], autouse=True)
 def attn_kernel(request, monkeypatch):
-    """Every case runs on all three kernels: the one-CTA-per-item default, the persistent kernel
-    and the CTA-pair (cta_group::2) one."""
+    """Every case runs on all four kernels: the one-CTA-per-item kernel, the same with every
+    tile's softmax spread over eight warps, the persistent kernel and the CTA-pair
+    (cta_group::2) one."""
     monkeypatch.setenv("SILE_CUDA_ATTN_KERNEL", request.param)
     return request.param
 
