@@ -477,7 +477,8 @@ int attention_launch(const AttnProblem& a, cudaStream_t stream) {
   // CTA per SM walking a queue of items, the next item's first Q K^T issued under the current
   // item's epilogue; measured 2-4 % behind on 4096- and 8192-long sequences, level at 1024),
   // =pair the CTA-pair kernel (attn_pair_sm100.cu: one Q tile per SM, K / V shared by the pair,
-  // three S buffers; its single softmax warp per scheduler is latency-bound, ~18 % behind).
+  // three S buffers; its single softmax warp per scheduler is latency-bound, ~18 % behind),
+  // =split the kernel with eight softmax warps per tile (attn_split_sm100.cu, ~10 % behind).
   // Read on every launch.
   const char* which = std::getenv("SILE_CUDA_ATTN_KERNEL");
   if (which && std::strcmp(which, "pair") == 0 && a.num_peers == 0) return attention_pair_launch(a, stream);
