@@ -740,7 +740,7 @@ def main():
         attention["e2e"] = {"value": afl / ae2e_s / 1e12, "unit": UNIT, "ms_per_step": ae2e_s * 1e3,
                             "h2d_bytes_per_step": 3 * q.numel() * 2, "d2h_bytes_per_step": q.numel() * 2,
                             "matches_device_result": bool(torch.equal(oh_, o_dev.cpu())),
-                            "api": "sile_cuda_launch_host (pinned host q, k, v in, o out)"}
+                            "api": "sile_cuda_launch_host (pinned host q, k, v in, o out; heads streamed in chunks, copies and kernels overlapped)"}
         del q, k, v, o_dev, qh_, kh_, vh_, oh_
         if not args.no_cpu_baseline:
             attention["cpu_baseline"] = attention_cpu_baseline(bh_total, s_len, True)

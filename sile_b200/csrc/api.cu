@@ -456,6 +456,98 @@ int read_and_clear_status() {
 // on a third, so the two PCIe directions and the tensor cores work at the same time.  Only for
 // launches that write every element of C (whole logical tiles, full grid), where chunking the
 // rows cannot change which elements are written.
+// The three streams (copies in, kernels, copies out) and the events of the host-buffer pipelines,
+// made once per host thread and device and reused by later calls.
+struct PipelineStreams {
+  int device = -1;
+  cudaStream_t in = nullptr, run = nullptr, out = nullptr;
+  std::vector<cudaEvent_t> events;
+};
+int pipeline_streams(PipelineStreams** out) {
+  static thread_local PipelineStreams cached;
+  int dev_now = 0;
+  SILE_CUDA_TRY(cudaGetDevice(&dev_now));
+  if (cached.device != dev_now) {
+    cached = PipelineStreams{};  // (streams and events of a previously used device are left to that device)
+    SILE_CUDA_TRY(cudaStreamCreateWithFlags(&cached.in, cudaStreamNonBlocking));
+    SILE_CUDA_TRY(cudaStreamCreateWithFlags(&cached.run, cudaStreamNonBlocking));
+    SILE_CUDA_TRY(cudaStreamCreateWithFlags(&cached.out, cudaStreamNonBlocking));
+    cached.device = dev_now;
+  }
+  *out = &cached;
+  return SILE_OK;
+}
+
+// Host-buffer attention over many heads: heads are independent, so q, k, v travel in chunks of
+// heads, each chunk's kernel starts when its copies have arrived and its o leaves while later
+// chunks are still arriving.  The step is then bounded by the host link (three inputs in, one
+// output back, full duplex) instead of being the sum of copies and kernel.
+int launch_host_attention_pipelined(const SileKernelDesc* d, void* const* host, const int64_t* shapes, int64_t ns, bool* handled) {
+  *handled = false;
+  if (d->in_dtype != SILE_DTYPE_BF16 || d->out_dtype != SILE_DTYPE_BF16) return SILE_OK;
+  const int64_t r = ns / 4;
+  if (ns % 4 != 0 || r < 3 || r > 4) return SILE_OK;
+  const int64_t dd = shapes[r - 1], sq = shapes[r - 2];
+  int64_t bh = 1;
+  for (int64_t i = 0; i + 2 < r; ++i) bh *= shapes[i];
+  const size_t head_bytes = static_cast<size_t>(sq) * dd * 2;
+  // chunks of about 8 MiB per tensor, at least 4 chunks; small problems take the plain path
+  const int64_t heads_per_chunk = std::max<int64_t>(1, static_cast<int64_t>((size_t(8) << 20) / std::max<size_t>(head_bytes, 1)));
+  if (dd != 128 || bh < 4 * heads_per_chunk || head_bytes * bh < (size_t(64) << 20)) return SILE_OK;
+  *handled = true;
+  PipelineStreams* streams = nullptr;
+  if (int prc = pipeline_streams(&streams)) return prc;
+  PipelineStreams& cached = *streams;
+  void* dev[4] = {nullptr, nullptr, nullptr, nullptr};
+  size_t events_used = 0;
+  int rc = SILE_OK;
+  auto check = [&](cudaError_t e, const char* what) {
+    if (e != cudaSuccess && rc == SILE_OK) rc = fail(SILE_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+    return e == cudaSuccess;
+  };
+  auto new_event = [&]() {
+    if (events_used == cached.events.size()) {
+      cudaEvent_t ev = nullptr;
+      check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
+      cached.events.push_back(ev);
+    }
+    return cached.events[events_used++];
+  };
+  for (int i = 0; i < 4 && rc == SILE_OK; ++i) rc = pool_alloc(&dev[i], head_bytes * bh, cached.in);
+  for (int64_t h0 = 0; h0 < bh && rc == SILE_OK; h0 += heads_per_chunk) {
+    const int64_t heads = std::min(heads_per_chunk, bh - h0);
+    const size_t off = head_bytes * h0, bytes = head_bytes * heads;
+    for (int i = 0; i < 3; ++i)
+      check(cudaMemcpyAsync(static_cast<char*>(dev[i]) + off, static_cast<const char*>(host[i]) + off, bytes, cudaMemcpyHostToDevice, cached.in),
+            "host->device copy");
+    cudaEvent_t arrived = new_event();
+    check(cudaEventRecord(arrived, cached.in), "cudaEventRecord");
+    check(cudaStreamWaitEvent(cached.run, arrived, 0), "cudaStreamWaitEvent");
+    if (rc != SILE_OK) break;
+    AttnProblem p;
+    p.q = static_cast<char*>(dev[0]) + off; p.k = static_cast<char*>(dev[1]) + off; p.v = static_cast<char*>(dev[2]) + off;
+    p.o = static_cast<char*>(dev[3]) + off;
+    p.bh = heads; p.s = sq; p.d = dd;
+    p.scale = d->scale;
+    p.causal = d->causal;
+    rc = attention_launch(p, cached.run);
+    if (rc != SILE_OK) break;
+    cudaEvent_t computed = new_event();
+    check(cudaEventRecord(computed, cached.run), "cudaEventRecord");
+    check(cudaStreamWaitEvent(cached.out, computed, 0), "cudaStreamWaitEvent");
+    check(cudaMemcpyAsync(static_cast<char*>(host[3]) + off, static_cast<char*>(dev[3]) + off, bytes, cudaMemcpyDeviceToHost, cached.out),
+          "device->host copy");
+  }
+  check(cudaStreamSynchronize(cached.in), "host->device copy");
+  check(cudaStreamSynchronize(cached.run), "kernel execution");
+  check(cudaStreamSynchronize(cached.out), "device->host copy");
+  if (rc == SILE_OK) rc = read_and_clear_status();
+  for (void* ptr : dev)
+    if (ptr) cudaFreeAsync(ptr, cached.in);
+  cudaStreamSynchronize(cached.in);
+  return rc;
+}
+
 int launch_host_matmul_pipelined(const SileKernelDesc* d, void* const* host, const int64_t* shapes, bool* handled) {
   *handled = false;
   const int64_t m = shapes[0], k = shapes[1], n = shapes[5];
@@ -473,22 +565,9 @@ int launch_host_matmul_pipelined(const SileKernelDesc* d, void* const* host, con
   if (m < 4 * rows || rows % bm != 0 || m % bm != 0 || static_cast<double>(m) * n * k < 1e11) return SILE_OK;
   *handled = true;
   const size_t in_sz = dtype_size(d->in_dtype), out_sz = dtype_size(d->out_dtype);
-  // The three streams are made once per host thread and device and reused by later calls.
-  struct Streams {
-    int device = -1;
-    cudaStream_t in = nullptr, run = nullptr, out = nullptr;
-    std::vector<cudaEvent_t> events;  // reused by every call of this thread
-  };
-  static thread_local Streams cached;
-  int dev_now = 0;
-  SILE_CUDA_TRY(cudaGetDevice(&dev_now));
-  if (cached.device != dev_now) {
-    cached = Streams{};  // (streams and events of a previously used device are left to that device)
-    SILE_CUDA_TRY(cudaStreamCreateWithFlags(&cached.in, cudaStreamNonBlocking));
-    SILE_CUDA_TRY(cudaStreamCreateWithFlags(&cached.run, cudaStreamNonBlocking));
-    SILE_CUDA_TRY(cudaStreamCreateWithFlags(&cached.out, cudaStreamNonBlocking));
-    cached.device = dev_now;
-  }
+  PipelineStreams* streams = nullptr;
+  if (int prc = pipeline_streams(&streams)) return prc;
+  PipelineStreams& cached = *streams;
   cudaStream_t s_in = cached.in, s_run = cached.run, s_out = cached.out;
   // Row chunks: full ones, then the last one halved down to 256 rows, so that what is left to do
   // after the last input row has arrived (one GEMM and one copy back) is small.
@@ -565,6 +644,14 @@ int launch_host(const SileKernelDesc* d, void* const* host, const int64_t* shape
   if (!host || !shapes) return fail(SILE_ERR_INVALID, "null argument");
   std::vector<ArgSpan> args;
   if (int rc = describe_args(d, shapes, ns, ntg, &args)) return rc;
+  if (d->op == SILE_OP_ATTENTION && host[0] && host[1] && host[2] && host[3]) {
+    bool handled = false;
+    const int rc = launch_host_attention_pipelined(d, host, shapes, ns, &handled);
+    if (handled) {
+      if (rc == SILE_OK) t_last_status = SILE_OK;
+      return rc;
+    }
+  }
   if (d->op == SILE_OP_MATMUL && !args[2].is_input && host[0] && host[1] && host[2]) {
     bool handled = false;
     const int rc = launch_host_matmul_pipelined(d, host, shapes, &handled);

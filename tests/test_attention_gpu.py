@@ -262,3 +262,22 @@ def test_fused_allgather_epilogue_on_one_gpu(sb, attn_kernel, causal):
     sb.synchronize()
     for b in bufs:
         assert torch.equal(b, want)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_host_buffer_launch_pipelines_head_chunks_and_matches_device_launch(sb, attn_kernel, causal):
+    """sile_cuda_launch_host streams a many-head attention in chunks of heads (copies in, kernels
+    and copies out overlapped); the result must equal the device-resident launch bit for bit.
+    72 heads x 3968 x 128: nine chunks of eight heads, the sequence not a multiple of the block."""
+    import torch
+    if attn_kernel != "single":
+        pytest.skip("one kernel is enough for the host pipeline")
+    bh, s = 72, 3968
+    g = torch.Generator().manual_seed(5)
+    q, k, v = [torch.randn(bh, s, 128, generator=g).to(torch.bfloat16).pin_memory() for _ in range(3)]
+    o_host = torch.zeros(bh, s, 128, dtype=torch.bfloat16).pin_memory()
+    sb.attention(q, k, v, o_host, 0.088, causal).apply_host()
+    o_dev = torch.zeros(bh, s, 128, device="cuda", dtype=torch.bfloat16)
+    sb.attention(q.cuda(), k.cuda(), v.cuda(), o_dev, 0.088, causal).apply()
+    sb.synchronize()
+    assert torch.equal(o_host, o_dev.cpu())
