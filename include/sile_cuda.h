@@ -172,6 +172,14 @@ int sile_cuda_matmul_shard(const SileKernelDesc* desc, const void* a, const void
                            int64_t m, int64_t n_total, int64_t k, int64_t n_begin, int64_t n_count,
                            void* stream);
 
+/* Diagnostic, host arithmetic only (no device needed): how the sliced 256 x 256 GEMM kernel
+ * would cut `tiles` tiles over `cta_pairs` resident CTA pairs when storing to `destinations`
+ * buffers, as text -- groups of "tiles x slices per tile", e.g. "18x2+222x1+16x2".
+ * `exchange_bound` != 0: the peers' share of the output takes longer to cross NVLink than the
+ * tiles take to compute.  No counterpart in the reference. */
+int sile_cuda_gemm_slice_plan(int32_t tiles, int32_t cta_pairs, int32_t destinations,
+                              int32_t exchange_bound, char* out, int64_t capacity);
+
 /* The same column-block matmul with the all-gather folded into its epilogue: rank
  * `rank` of `world` (<= 8) computes its block and stores every element into the
  * full [M, n_total] row-major buffer of EVERY rank.  c_peers[i] is the base of

@@ -19,7 +19,7 @@ EXPORTED_SYMBOLS = (
     "sile_kernel_matmul", "sile_kernel_matmul_acc", "sile_kernel_vec_add", "sile_kernel_relu", "sile_kernel_softmax",
     "sile_kernel_parallel_reduce", "sile_kernel_matvec", "sile_kernel_attention", "sile_cuda_bind_consts", "sile_cuda_bind_scale",
     "sile_cuda_launch", "sile_cuda_launch_host", "sile_cuda_matmul_shard",
-    "sile_cuda_matmul_allgather", "sile_cuda_attention_allgather", "sile_cuda_unshard_columns", "sile_cuda_matmul_f32_noalloc", "sile_cuda_set_device",
+    "sile_cuda_matmul_allgather", "sile_cuda_attention_allgather", "sile_cuda_unshard_columns", "sile_cuda_matmul_f32_noalloc", "sile_cuda_set_device", "sile_cuda_gemm_slice_plan",
     "sile_cuda_device_count", "sile_cuda_synchronize", "sile_cuda_decode_status", "sile_cuda_malloc", "sile_cuda_free",
     "sile_cuda_memcpy_h2d", "sile_cuda_memcpy_d2h", "sile_cuda_memset", "sile_cuda_stream_create",
     "sile_cuda_stream_destroy", "sile_cuda_matmul_workspace_bytes",
@@ -63,6 +63,8 @@ def lib() -> C.CDLL:
                                         C.POINTER(C.c_uint32)]
     L.sile_cuda_matmul_shard.argtypes = [C.POINTER(KernelDesc), C.c_void_p, C.c_void_p, C.c_void_p,
                                          _i64, _i64, _i64, _i64, _i64, C.c_void_p]
+    L.sile_cuda_gemm_slice_plan.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_char_p, C.c_int64]
+    L.sile_cuda_gemm_slice_plan.restype = C.c_int
     L.sile_cuda_matmul_allgather.argtypes = [C.POINTER(KernelDesc), C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p),
                                              C.c_int32, C.c_int32, _i64, _i64, _i64, C.c_void_p]
     L.sile_cuda_attention_allgather.argtypes = [C.POINTER(KernelDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p),

@@ -39,11 +39,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not is_stale():
         return LIB_PATH
     os.makedirs(LIB_DIR, exist_ok=True)
+    tmp = LIB_PATH + ".tmp"  # linked beside the target and renamed over it: a reader never sees half a library
     cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [
-        "-o", LIB_PATH] + [os.path.join(CSRC, s) for s in SOURCES]
+        "-o", tmp] + [os.path.join(CSRC, s) for s in SOURCES]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+    os.replace(tmp, LIB_PATH)
     if verbose:
         sys.stderr.write(proc.stderr)
     return LIB_PATH

@@ -721,6 +721,10 @@ extern "C" {
 
 int sile_cuda_version(void) { return 100; }
 
+int sile_cuda_gemm_slice_plan(int32_t tiles, int32_t cta_pairs, int32_t destinations, int32_t exchange_bound, char* out, int64_t capacity) {
+  return gemm_slice_plan_text(tiles, cta_pairs, destinations, exchange_bound, out, capacity > 0 ? static_cast<size_t>(capacity) : 0);
+}
+
 const char* sile_cuda_last_error(void) { return t_last_error.c_str(); }
 const char* sile_cuda_last_kernel(void) { return t_last_kernel; }
 int sile_cuda_last_status(void) { return t_last_status; }

@@ -1429,6 +1429,25 @@ AgPlan make_ag_plan(int tiles, int clusters, bool bf16, bool stagger, bool excha
   return plan;
 }
 
+// The plan a launch would take, as text ("18x2+222x1+16x2": tiles x slices per tile, group by
+// group), without launching anything.
+AgPlan choose_ag_plan(int tiles, int clusters, bool bf16, int destinations, bool exchange_bound) {
+  AgPlan plan = make_ag_plan(tiles, clusters, bf16, false, false);
+  if (destinations > 1) {
+    const AgPlan staggered = make_ag_plan(tiles, clusters, bf16, true, exchange_bound);
+    if (exchange_bound || ag_makespan(staggered, clusters) <= 1.01 * ag_makespan(plan, clusters)) plan = staggered;
+  }
+  return plan;
+}
+
+int format_ag_plan(const AgPlan& plan, char* out, size_t cap) {
+  int len = 0;
+  if (cap > 0) out[0] = 0;
+  for (int g = 0; g < plan.groups && len < static_cast<int>(cap) - 16; ++g)
+    len += snprintf(out + len, cap - len, "%s%dx%d", g ? "+" : "", plan.n[g], 1 << plan.s[g]);
+  return len;
+}
+
 template <typename OutT>
 int launch_pair_ag(const CUtensorMap& ta, const AgBMaps& tb, const GemmParams& gp, bool bf16, int vec_ok, int* status,
                    cudaStream_t stream, const PeerOut& peers, const OutMaps& out_maps) {
@@ -1438,16 +1457,11 @@ int launch_pair_ag(const CUtensorMap& ta, const AgBMaps& tb, const GemmParams& g
   // Several destinations: the staggered head, unless it makes the busiest CTA pair finish later
   // and the exchange is not what bounds the step anyway (rates measured for this kernel on 8192^3
   // over 4 and 8 GPUs: 0.58 TB/s of peer stores leaving a GPU, 1.4 PFLOP/s of tensor work).
-  AgPlan plan = make_ag_plan(tiles, max_clusters, bf16, false, false);
-  if (peers.count > 1) {
-    const double k_total = static_cast<double>(gp.k_blocks_per_seg) * gp.num_segs * kBK;
-    const double out_elems = static_cast<double>(gp.m_valid) * gp.n_valid;
-    const double link_s = out_elems * sizeof(OutT) * (peers.count - 1) / 0.58e12;
-    const double math_s = 2.0 * out_elems * k_total / 1.4e15;
-    const bool exchange_bound = link_s > math_s;
-    const AgPlan staggered = make_ag_plan(tiles, max_clusters, bf16, true, exchange_bound);
-    if (exchange_bound || ag_makespan(staggered, max_clusters) <= 1.01 * ag_makespan(plan, max_clusters)) plan = staggered;
-  }
+  const double k_total = static_cast<double>(gp.k_blocks_per_seg) * gp.num_segs * kBK;
+  const double out_elems = static_cast<double>(gp.m_valid) * gp.n_valid;
+  const double link_s = out_elems * sizeof(OutT) * (peers.count - 1) / 0.58e12;
+  const double math_s = 2.0 * out_elems * k_total / 1.4e15;
+  const AgPlan plan = choose_ag_plan(tiles, max_clusters, bf16, peers.count, link_s > math_s);
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1463,9 +1477,8 @@ int launch_pair_ag(const CUtensorMap& ta, const AgBMaps& tb, const GemmParams& g
   SILE_CUDA_TRY(cudaLaunchKernelEx(&cfg, &gemm_tn_pair_sliced_kernel<OutT>, ta, tb, gp, plan, vec_ok, status, peers, out_maps));
   // name, then the plan: tiles x slices per group, e.g. "plan=18x2+222x1+16x2"
   char name[160];
-  int len = snprintf(name, sizeof(name), "%s plan=", sizeof(OutT) == 4 ? "gemm_tn_pair_sliced_kernel<float>" : "gemm_tn_pair_sliced_kernel<16-bit>");
-  for (int g = 0; g < plan.groups && len < static_cast<int>(sizeof(name)) - 16; ++g)
-    len += snprintf(name + len, sizeof(name) - len, "%s%dx%d", g ? "+" : "", plan.n[g], 1 << plan.s[g]);
+  const int len = snprintf(name, sizeof(name), "%s plan=", sizeof(OutT) == 4 ? "gemm_tn_pair_sliced_kernel<float>" : "gemm_tn_pair_sliced_kernel<16-bit>");
+  format_ag_plan(plan, name + len, sizeof(name) - len);
   note_kernel(name, cfg.gridDim.x, cfg.blockDim.x, cfg.dynamicSmemBytes);
   return SILE_OK;
 }
@@ -1511,6 +1524,12 @@ size_t gemm_workspace_bytes(const GemmProblem& p) {
   }
   if (p.b_layout == SILE_LAYOUT_ROW_MAJOR) return static_cast<size_t>(p.n * e.kp) * 2;  // B^T
   return 0;
+}
+
+int gemm_slice_plan_text(int tiles, int clusters, int destinations, int exchange_bound, char* out, size_t cap) {
+  if (tiles <= 0 || clusters <= 0 || destinations < 1 || !out || cap < 32) return fail(SILE_ERR_INVALID, "slice plan: bad argument");
+  format_ag_plan(choose_ag_plan(tiles, clusters, true, destinations, exchange_bound != 0), out, cap);
+  return SILE_OK;
 }
 
 int gemm_launch(const GemmProblem& p, cudaStream_t stream) {

@@ -78,6 +78,8 @@ struct GemmProblem {
 };
 size_t gemm_workspace_bytes(const GemmProblem& p);
 int gemm_launch(const GemmProblem& p, cudaStream_t stream);
+// Text of the slice plan the sliced / all-gather GEMM kernel would take (host arithmetic only).
+int gemm_slice_plan_text(int tiles, int clusters, int destinations, int exchange_bound, char* out, size_t cap);
 
 // dst[r, j*cols + c] = src[j, r, c]: lays the rank-major result of an all-gather of column
 // blocks out as one row-major matrix.
