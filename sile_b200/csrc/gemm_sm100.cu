@@ -521,7 +521,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 //
 // Work items are tiles or column slices of tiles, in consecutive groups each cut into 2^s slices
 // of 256 >> s columns (s = 0, 1 or 2): a slice is an MMA of that N fed by (128 >> s) rows of B per
-// CTA and stored as (4 >> s) boxes.  Item i goes to CTA pair i mod (pairs).  Slicing the tiles of
+// CTA and stored as (4 >> s) boxes per warp (16-bit outputs; twice as many 32-column boxes for
+// f32).  Item i goes to CTA pair i mod (pairs).  Slicing the tiles of
 // the last, partly filled wave halves the time that wave takes (256 tiles on 74 CTA pairs are 3.5
 // waves instead of 4); with several destinations a few sliced tiles at the head put the CTA
 // pairs out of step with one another, so that their store bursts do not all hit NVLink at once.
