@@ -276,7 +276,10 @@ def test_host_buffer_launch_pipelines_head_chunks_and_matches_device_launch(sb, 
     g = torch.Generator().manual_seed(5)
     q, k, v = [torch.randn(bh, s, 128, generator=g).to(torch.bfloat16).pin_memory() for _ in range(3)]
     o_host = torch.zeros(bh, s, 128, dtype=torch.bfloat16).pin_memory()
-    sb.attention(q, k, v, o_host, 0.088, causal).apply_host()
+    if causal:   # the same buffers described as rank 4, [batch, heads, S, D]
+        sb.attention(q.view(2, 36, s, 128), k.view(2, 36, s, 128), v.view(2, 36, s, 128), o_host.view(2, 36, s, 128), 0.088, causal).apply_host()
+    else:
+        sb.attention(q, k, v, o_host, 0.088, causal).apply_host()
     o_dev = torch.zeros(bh, s, 128, device="cuda", dtype=torch.bfloat16)
     sb.attention(q.cuda(), k.cuda(), v.cuda(), o_dev, 0.088, causal).apply()
     sb.synchronize()
