@@ -1362,7 +1362,9 @@ double ag_makespan(const AgPlan& plan, int clusters) {
 // two, so half of the CTA pairs finish their first item after 0.7 of a tile time and stay 0.3 of a
 // tile time ahead of the others; the waves' store bursts then reach NVLink in two halves
 // (8192^3: 0.240 ms against 0.264 over 4 GPUs, 0.247 against 0.256 over 8; cutting a half wave,
-// which leaves all pairs in step, was slower than no cut at all).
+// which leaves all pairs in step, was slower than no cut at all).  With `exchange_bound` as well
+// (the peers' share of the output takes longer to cross NVLink than the tiles take to compute) the
+// head puts the pairs into three phases instead (0.2405 ms over 8 GPUs).
 // SILE_CUDA_GEMM_AG_SPLIT = off | s0,n0,s1,n1,...,s_last overrides it (tuning, tests): n0 tiles
 // in 2^s0 slices, the next n1 in 2^s1, ..., the rest in 2^s_last; a negative n = the whole waves
 // of what is left.
@@ -1405,6 +1407,17 @@ AgPlan make_ag_plan(int tiles, int clusters, bool bf16, bool stagger, bool excha
         from_env = true;
       }
     }
+  }
+  if (!from_env && stagger && exchange_bound && tiles > clusters) {
+    // Three phases: two thirds of the pairs start with a half tile, half of those follow it with
+    // a second one, the last third starts with a whole tile; first stores after 0.7, 1.0 and 1.4
+    // tile times.  Whole tiles after that (the tail's cut does not matter: compute is not the bound).
+    const int h1 = clusters / 3;
+    add(h1, 1);
+    add(clusters - 2 * h1, 0);
+    add(h1 / 2, 1);
+    add(left, 0);
+    from_env = true;  // plan complete
   }
   if (!from_env) {
     if (stagger && tiles > clusters) add(clusters / 4, 1);

@@ -51,8 +51,9 @@ def test_status_word_maps_to_timeout_error(lib):
 def test_slice_plans_of_the_sharded_headline_gemm(lib):
     """Host arithmetic of the sliced GEMM kernel's work plan, for one rank's block of the 8192^3
     GEMM on 74 CTA pairs: 2 GPUs -- whole tiles (a staggered head would add a round); 4 GPUs -- a
-    quarter wave cut in two at the head, the last wave cut in two; 8 GPUs (exchange-bound) -- the
-    same head, the rest of the second wave cut in two; one destination -- only the last wave."""
+    quarter wave cut in two at the head, the last wave cut in two; 8 GPUs (exchange-bound) -- a
+    three-phase head (half tiles for two thirds of the pairs, a second half tile for half of
+    those), whole tiles after it; one destination -- only the last wave."""
     import ctypes as C
 
     def plan(tiles, dest, exchange_bound):
@@ -62,7 +63,7 @@ def test_slice_plans_of_the_sharded_headline_gemm(lib):
 
     assert plan(512, 2, False) == "444x1+68x1"
     assert plan(256, 4, False) == "18x2+222x1+16x2"
-    assert plan(128, 8, True) == "18x2+74x1+36x2"
+    assert plan(128, 8, True) == "24x2+26x1+12x2+66x1"
     assert plan(256, 1, False) == "222x1+34x2"
     assert plan(128, 1, False) == "74x1+54x1"
     for text, tiles in ((plan(t, d, e), t) for t in (1, 73, 74, 75, 300, 1024) for d in (1, 4) for e in (False, True)):
