@@ -1382,11 +1382,11 @@ AgPlan make_ag_plan(int tiles, int clusters, bool bf16, bool stagger, bool excha
     left -= n;
     ++g;
   };
-  bool from_env = false;
+  bool planned = false;
   if (const char* e = getenv("SILE_CUDA_GEMM_AG_SPLIT")) {
     if (!strcmp(e, "off")) {
       add(tiles, 0);
-      from_env = true;
+      planned = true;
     } else {
       long v[2 * kAgMaxGroups - 1];
       int count = 0;
@@ -1404,11 +1404,11 @@ AgPlan make_ag_plan(int tiles, int clusters, bool bf16, bool stagger, bool excha
       if (ok) {
         for (int i = 0; i + 1 < count; i += 2) add(v[i + 1] < 0 ? whole_waves(left) : static_cast<int>(v[i + 1]), static_cast<int>(v[i]));
         add(left, static_cast<int>(v[count - 1]));
-        from_env = true;
+        planned = true;
       }
     }
   }
-  if (!from_env && stagger && exchange_bound && tiles > clusters) {
+  if (!planned && stagger && exchange_bound && tiles > clusters) {
     // Three phases: two thirds of the pairs start with a half tile, half of those follow it with
     // a second one, the last third starts with a whole tile; first stores after 0.7, 1.0 and 1.4
     // tile times.  Whole tiles after that (the tail's cut does not matter: compute is not the bound).
@@ -1417,14 +1417,14 @@ AgPlan make_ag_plan(int tiles, int clusters, bool bf16, bool stagger, bool excha
     add(clusters - 2 * h1, 0);
     add(h1 / 2, 1);
     add(left, 0);
-    from_env = true;  // plan complete
+    planned = true;
   }
-  if (!from_env) {
+  if (!planned) {
     if (stagger && tiles > clusters) add(clusters / 4, 1);
     add(whole_waves(left), 0);
     // The tail's cut: the one with which the busiest pair finishes soonest (the head may have
-    // shifted the tail off a wave boundary); when the exchange bounds the step, as fine as one
-    // wave allows, for smaller last stores.
+    // shifted the tail off a wave boundary); when the exchange bounds the step (here: fewer tiles
+    // than CTA pairs), as fine as one wave allows, for smaller last stores.
     int cut = ag_tail_cut(left, clusters, nullptr);
     if (!exchange_bound && left > 0) {
       double best = 0.0;
