@@ -42,7 +42,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # that kernel for the workload (sile_cuda_last_kernel); if the choice changes the bench stops
 # instead of attaching a stale number to another kernel.
 NCU_DRAM_TRAFFIC = {
-    ("gemm_bf16_8192", "gemm_tn_pair_wide_kernel<16-bit>"): 1.046e9,
+    ("gemm_bf16_8192", "gemm_tn_pair_wide_kernel<16-bit>"): 0.991e9,
     ("attn_fwd_b8_h32_s8192_d128_causal", "attn_fwd_kernel"): 2.170e9,
     ("attn_fwd_b4_h32_s4096_d128_noncausal", "attn_fwd_kernel"): 0.5348e9,
 }
